@@ -1,0 +1,166 @@
+/*
+ * lasp_b200 - C ABI of the B200 (sm_100a) linear-attention library.
+ *
+ * The reference (OpenNLPLab/LASP) has no FFI layer: its Python autograd
+ * functions launch Triton kernels directly.  This header is the boundary the
+ * Python operator surface of this repository binds with ctypes; every entry
+ * point names the reference launcher / kernel whose work it takes over
+ * (paths relative to the reference checkout).
+ *
+ * Conventions
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer unless
+ *     its name ends in _host;
+ *   - the caller owns all memory; nothing here allocates device memory;
+ *   - every call is asynchronous on the given stream (a cudaStream_t passed
+ *     as void*; NULL = the legacy default stream);
+ *   - return value: LASP_OK or a negative lasp_status; invalid arguments are
+ *     rejected BEFORE anything is launched;
+ *   - tensors are contiguous: q,k (b,h,n,d); v,o,do (b,h,n,e); s h floats;
+ *     rank states kv_in/kv_out/dkv_in/dkv_out (b,h,d,e) fp32.
+ *
+ * Math (per batch, head; lambda = exp(-s_h)):
+ *   O  = ((Q K^T) * M) V + diag(lambda^pos) Q KV_in,   M_ij = lambda^(i-j) [i>=j]
+ *   KV_out  = lambda^n KV_in  + sum_j lambda^(n-j) k_j v_j^T
+ *   DKV_out = lambda^n DKV_in + sum_i lambda^i     q_i do_i^T
+ * The sequence is cut into chunks; each phase below is one kernel launch:
+ *   chunk states (independent of the incoming rank state) -> scan over chunks
+ *   (consumes KV_in, yields KV_out) -> outputs.  The split lets a
+ *   sequence-parallel caller overlap the first phase with the state transfer.
+ */
+#ifndef LASP_B200_H
+#define LASP_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LASP_B200_ABI_VERSION 1
+
+typedef enum {
+  LASP_OK = 0,
+  LASP_ERR_NULL = -1,       /* a required pointer is NULL */
+  LASP_ERR_SHAPE = -2,      /* unsupported b,h,n,d,e */
+  LASP_ERR_DTYPE = -3,      /* unknown dtype */
+  LASP_ERR_ALIGN = -4,      /* a pointer is not 16-byte aligned */
+  LASP_ERR_WORKSPACE = -5,  /* workspace too small */
+  LASP_ERR_CUDA = -6,       /* a CUDA runtime call failed (see lasp_b200_last_cuda_error) */
+  LASP_ERR_PATH = -7,       /* requested kernel path cannot run this problem */
+  LASP_ERR_DEVICE = -8,     /* a kernel reported a fault (see lasp_b200_read_status) */
+  LASP_ERR_TOO_LARGE = -9   /* problem exceeds a fixed capacity of the entry point */
+} lasp_status;
+
+typedef enum { LASP_F32 = 0, LASP_BF16 = 1, LASP_F16 = 2 } lasp_dtype;
+
+/* which kernels run: AUTO picks TENSOR when the problem qualifies */
+typedef enum {
+  LASP_PATH_AUTO = 0,
+  LASP_PATH_SIMT = 1,   /* fp32 FFMA kernels: any dtype, d,e multiples of 16 up to 128, any n */
+  LASP_PATH_TENSOR = 2  /* tcgen05/TMEM/TMA kernels: bf16, d,e in {64,128}, n multiple of 128 */
+} lasp_path;
+
+typedef struct {
+  int32_t b, h, n, d, e;
+  int32_t dtype;  /* lasp_dtype of q,k,v,o,do,dq,dk,dv */
+  int32_t path;   /* lasp_path */
+  int32_t reserved;
+} lasp_problem;
+
+/* Forward arguments.  ws = workspace of lasp_b200_fwd_workspace_bytes(); after
+ * the scan phase it holds the per-chunk prefix states, which the backward
+ * reads (the "intermediate state caching" of lasp/lasp_fuse_parallel.py:876,
+ * 1103) - keep it alive until backward has run. */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  const float* s;
+  const float* kv_in; /* NULL = zero state (first rank / single device) */
+  float* kv_out;      /* NULL = not wanted */
+  void* o;
+  void* ws;
+  size_t ws_bytes;
+} lasp_fwd_args;
+
+/* Backward arguments.  fwd_ws = the forward's workspace (read only);
+ * ws = scratch of lasp_b200_bwd_workspace_bytes(). */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* d_o;
+  const float* s;
+  const float* dkv_in; /* NULL = zero state (last rank / single device) */
+  float* dkv_out;      /* NULL = not wanted */
+  void* dq;
+  void* dk;
+  void* dv;
+  const void* fwd_ws;
+  size_t fwd_ws_bytes;
+  void* ws;
+  size_t ws_bytes;
+} lasp_bwd_args;
+
+int lasp_b200_abi_version(void);
+const char* lasp_b200_strerror(int status);
+/* text of the last CUDA runtime error seen by this thread inside the library */
+const char* lasp_b200_last_cuda_error(void);
+
+/* Resolves LASP_PATH_AUTO; returns LASP_PATH_SIMT / LASP_PATH_TENSOR or a
+ * negative status when the problem is invalid (lasp_forward's shape asserts,
+ * lasp/lasp_fuse_parallel.py:1080-1085, made explicit). */
+int lasp_b200_resolve_path(const lasp_problem* p);
+/* tokens per chunk state for the resolved path */
+int lasp_b200_chunk_tokens(const lasp_problem* p);
+size_t lasp_b200_fwd_workspace_bytes(const lasp_problem* p);
+size_t lasp_b200_bwd_workspace_bytes(const lasp_problem* p);
+
+/* ---- forward phases -------------------------------------------------- */
+/* per-chunk local states sum_c lambda^(len-c) k_c v_c^T.
+ * Replaces _fwd_kv_parallel, lasp/lasp_fuse_parallel.py:117-200. */
+int lasp_b200_fwd_chunk_states(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
+/* exclusive decayed scan of the chunk states seeded with kv_in; writes kv_out.
+ * Replaces _fwd_kv_reduce, lasp/lasp_fuse_parallel.py:203-257, and the host
+ * update KV = block_decay*KV + kv, lasp/lasp_fuse_parallel.py:941-942. */
+int lasp_b200_fwd_scan(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
+/* O = intra-chunk masked product + decayed Q x prefix state.
+ * Replaces _fwd_diag_kernel + _fwd_none_diag_kernel,
+ * lasp/lasp_fuse_parallel.py:15-114,261-336 (== _fwd_kernel of
+ * lasp/lightning_attention.py:6-83 and lasp/lasp_fuse.py:15-127). */
+int lasp_b200_fwd_output(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
+/* the three phases back to back: lasp_forward, lasp/lasp_fuse.py:356-406 */
+int lasp_b200_forward(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
+
+/* ---- backward phases ------------------------------------------------- */
+/* per-chunk local dKV states sum_r lambda^r q_r do_r^T.
+ * Replaces _bwd_dkv_parallel, lasp/lasp_fuse_parallel.py:522-604. */
+int lasp_b200_bwd_chunk_states(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
+/* reverse exclusive decayed scan seeded with dkv_in; writes dkv_out.
+ * Replaces _bwd_dkv_reduce, lasp/lasp_fuse_parallel.py:607-662, and the host
+ * update DKV = block_decay*DKV + dkv, lasp/lasp_fuse_parallel.py:1067-1068. */
+int lasp_b200_bwd_scan(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
+/* dQ, dK, dV from the cached prefix states and the suffix dKV states.
+ * Replaces _bwd_diag_kernel + _bwd_none_diag_kernel,
+ * lasp/lasp_fuse_parallel.py:339-519,665-830 (== _bwd_intra_kernel +
+ * _bwd_inter_kernel, lasp/lightning_attention.py:86-393). */
+int lasp_b200_bwd_grads(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
+/* the three phases back to back: lasp_backward, lasp/lasp_fuse.py:409-475 */
+int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
+
+/* x_out = exp(-s_h n) x_in + x_local on (b,h,d,e) fp32 states; x_in may be NULL.
+ * Replaces the torch glue KV = block_decay*KV + kv, lasp/lasp_naive.py:565,614. */
+int lasp_b200_state_combine(int b, int h, int d, int e, int n, const float* s, const float* x_in,
+                            const float* x_local, float* x_out, void* stream);
+
+/* Copies this device's sticky kernel-fault word to *status_host (synchronises
+ * the stream) and clears it when clear != 0.  0 = no kernel reported a fault;
+ * the tensor-core kernels set bits when one of their bounded waits (TMA
+ * arrival, tcgen05 completion) runs out instead of spinning for ever. */
+int lasp_b200_read_status(int32_t* status_host, int clear, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LASP_B200_H */

@@ -1,0 +1,12 @@
+"""lasp_b200: LASP's linear-attention operators on hand-written sm_100a CUDA.
+
+Same names and signatures as the reference's ``lasp`` package.
+"""
+from .lasp_cache import lasp_cache, lasp_cache_  # noqa: F401
+from .lasp_fuse import lasp_fuse, lasp_fuse_  # noqa: F401
+from .lasp_fuse_parallel import lasp_fuse_parallel, lasp_fuse_parallel_  # noqa: F401
+from .lasp_naive import lasp_naive, lasp_naive_  # noqa: F401
+from .lightning_attention import lightning_attn, lightning_attn_  # noqa: F401
+from .utils import *  # noqa: F401,F403
+
+__version__ = "0.1.0"

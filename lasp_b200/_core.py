@@ -1,0 +1,169 @@
+"""Shared machinery of the five operators: head-dim slicing, the single-device
+autograd function and the sequence-parallel autograd function.
+
+The kernels are reached through ``ENGINE`` (module ``lasp_b200.engine``, the
+ctypes launcher of the CUDA library).  The host-logic tests replace ``ENGINE``
+with a stand-in to exercise group mapping and message order on gloo ranks; the
+product has no other backend.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import comm
+from . import engine as ENGINE  # noqa: N812  (replaced as a whole by host-logic tests)
+from .utils.seq_parallel_manager import (
+    get_seq_parallel_receive_rank,
+    get_seq_parallel_send_rank,
+    get_sequence_parallel_group,
+    get_sequence_parallel_rank,
+    get_sequence_parallel_world_size,
+)
+
+MAX_HEAD_SLICE = 128  # widest q/k (d) or v (e) slice one kernel call takes
+
+
+def _cuts(width: int):
+    """[0, 128, 256, ..., width]: slice borders of a head dimension."""
+    edges = list(range(0, width, MAX_HEAD_SLICE)) + [width]
+    return list(zip(edges[:-1], edges[1:]))
+
+
+def sliced_apply(fn, q, k, v, state_bufs=()):
+    """Head-dim slicing of the reference wrappers (lasp/lightning_attention.py:510-531):
+    the op is a sum over 128-wide q,k slices.  Wider v than 128 is handled the
+    same way in the other direction (outputs of v slices are concatenated).
+    ``state_bufs`` are (b,h,d,e) buffers sliced alongside.
+    """
+    d, e = q.shape[-1], v.shape[-1]
+    outs = []
+    for e0, e1 in _cuts(e):
+        vs = v if (e0, e1) == (0, e) else v[..., e0:e1]
+        acc = None
+        for d0, d1 in _cuts(d):
+            whole = (d0, d1) == (0, d)
+            qs = q if whole else q[..., d0:d1]
+            ks = k if whole else k[..., d0:d1]
+            bufs = [x if (whole and (e0, e1) == (0, e)) else x[:, :, d0:d1, e0:e1].contiguous() for x in state_bufs]
+            o = fn(qs, ks, vs, *bufs)
+            acc = o if acc is None else acc + o
+        outs.append(acc)
+    return outs[0] if len(outs) == 1 else torch.cat(outs, dim=-1)
+
+
+def _plan_for(q, v, path=None):
+    b, h, n, d = q.shape
+    return ENGINE.make_plan(b, h, n, d, v.shape[-1], q.dtype, path)
+
+
+def _check_shapes(q, k, v, s):
+    if q.dim() != 4 or k.shape != q.shape or v.dim() != 4 or v.shape[:3] != q.shape[:3]:
+        raise ValueError(f"expected q,k (b,h,n,d) and v (b,h,n,e); got {tuple(q.shape)}, {tuple(k.shape)}, "
+                         f"{tuple(v.shape)}")
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise TypeError("q, k, v must share one dtype")
+    if s.numel() != q.shape[1]:
+        raise ValueError(f"decay tensor has {s.numel()} entries for {q.shape[1]} heads")
+
+
+class LightningAttention(torch.autograd.Function):
+    """Single-device op: O = ((Q K^T) * M) V.  Interface of LightningAttention,
+    lasp/lightning_attention.py:396-504; gradients for q, k, v only."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, s):
+        _check_shapes(q, k, v, s)
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        plan = _plan_for(q, v)
+        fw = ENGINE.Forward(plan, q, k, v, s)
+        o = fw.run()
+        ctx.plan = plan
+        ctx.fwd_ws = fw.ws
+        ctx.save_for_backward(q, k, v, s)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, s = ctx.saved_tensors
+        bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws)
+        dq, dk, dv = bw.run()
+        return dq, dk, dv, None
+
+
+class SequenceParallelAttention(torch.autograd.Function):
+    """Sequence-parallel op shared by lasp_naive / lasp_cache / lasp_fuse /
+    lasp_fuse_parallel (LaspNaive ... LaspFuseParallel of the reference, e.g.
+    lasp/lasp_fuse_parallel.py:1073-1137).
+
+    Each rank holds one contiguous chunk of the sequence.  Forward: the KV
+    state arrives from the previous rank, the outgoing state leaves for the
+    next; backward: dKV travels the other way.  ``overlap`` chooses between the
+    reference's order (receive, compute, send) and the overlapped one (post the
+    receive, run the state-independent chunk-state kernel, wait, scan, send,
+    then the output kernel).
+    """
+
+    @staticmethod
+    def forward(ctx, q, k, v, s, KV, DKV, overlap):
+        _check_shapes(q, k, v, s)
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        b, h, n, d = q.shape
+        e = v.shape[-1]
+        for name, buf in (("KV", KV), ("DKV", DKV)):
+            if tuple(buf.shape) != (b, h, d, e) or buf.dtype != torch.float32 or not buf.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous float32 tensor of shape {(b, h, d, e)}")
+        group = get_sequence_parallel_group()
+        rank = get_sequence_parallel_rank()
+        last = get_sequence_parallel_world_size() - 1
+        prev_rank, next_rank = get_seq_parallel_send_rank(), get_seq_parallel_receive_rank()
+        link = comm.StateLink(group)
+
+        plan = _plan_for(q, v)
+        fw = ENGINE.Forward(plan, q, k, v, s, kv_in=KV if rank > 0 else None, kv_out=KV if rank < last else None)
+        if overlap:
+            pending = link.post_recv(KV, prev_rank) if rank > 0 else None
+            fw.chunk_states()
+            link.wait(pending)
+            fw.scan()
+            sent = link.post_send(KV, next_rank) if rank < last else None
+            fw.output()
+            link.wait(sent)
+        else:
+            if rank > 0:
+                link.recv(KV, prev_rank)
+            fw.run()
+            if rank < last:
+                link.send(KV, next_rank)
+
+        ctx.plan, ctx.fwd_ws, ctx.DKV, ctx.overlap = plan, fw.ws, DKV, overlap
+        ctx.link, ctx.rank, ctx.last = link, rank, last
+        ctx.prev_rank, ctx.next_rank = prev_rank, next_rank
+        ctx.save_for_backward(q, k, v, s)
+        return fw.o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, s = ctx.saved_tensors
+        DKV, link, rank, last = ctx.DKV, ctx.link, ctx.rank, ctx.last
+        bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws,
+                             dkv_in=DKV if rank < last else None, dkv_out=DKV if rank > 0 else None)
+        if ctx.overlap:
+            pending = link.post_recv(DKV, ctx.next_rank) if rank < last else None
+            bw.chunk_states()
+            link.wait(pending)
+            bw.scan()
+            sent = link.post_send(DKV, ctx.prev_rank) if rank > 0 else None
+            bw.grads()
+            link.wait(sent)
+        else:
+            if rank < last:
+                link.recv(DKV, ctx.next_rank)
+            bw.run()
+            if rank > 0:
+                link.send(DKV, ctx.prev_rank)
+        return bw.dq, bw.dk, bw.dv, None, None, None, None
+
+
+def sequence_parallel(q, k, v, s, KV, DKV, overlap: bool):
+    return sliced_apply(lambda qs, ks, vs, kv, dkv: SequenceParallelAttention.apply(qs, ks, vs, s, kv, dkv, overlap),
+                        q, k, v, (KV, DKV))

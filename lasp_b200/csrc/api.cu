@@ -1,0 +1,211 @@
+// extern "C" entry points of liblasp_b200.so: argument validation, workspace
+// layout and the choice between the tensor-core and the fp32 kernels.
+#include <string.h>
+
+#include "common.cuh"
+
+namespace {
+
+thread_local char g_cuda_error[256] = "";
+
+int cuda_fail(cudaError_t err) {
+  if (err == cudaSuccess) return LASP_OK;
+  strncpy(g_cuda_error, cudaGetErrorString(err), sizeof(g_cuda_error) - 1);
+  g_cuda_error[sizeof(g_cuda_error) - 1] = 0;
+  return LASP_ERR_CUDA;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// validates the problem and fills Dims; returns LASP_OK or a negative status
+int make_dims(const lasp_problem* p, lasp::Dims* m) {
+  if (!p) return LASP_ERR_NULL;
+  if (p->dtype != LASP_F32 && p->dtype != LASP_BF16 && p->dtype != LASP_F16) return LASP_ERR_DTYPE;
+  if (p->b <= 0 || p->h <= 0 || p->n <= 0 || p->d <= 0 || p->e <= 0) return LASP_ERR_SHAPE;
+  if (p->d % 16 || p->e % 16 || p->d > 128 || p->e > 128) return LASP_ERR_SHAPE;
+  if ((long long)p->b * p->h > 65535) return LASP_ERR_SHAPE;
+  m->b = p->b; m->h = p->h; m->n = p->n; m->d = p->d; m->e = p->e;
+  m->dtype = p->dtype;
+  m->chunk = lasp::kTensorChunk;
+  m->nc = (p->n + m->chunk - 1) / m->chunk;
+  const bool tensor_ok = lasp::tensor_path_supported(*m);
+  int path = p->path;
+  if (path == LASP_PATH_AUTO) path = tensor_ok ? LASP_PATH_TENSOR : LASP_PATH_SIMT;
+  if (path == LASP_PATH_TENSOR && !tensor_ok) return LASP_ERR_PATH;
+  if (path != LASP_PATH_TENSOR && path != LASP_PATH_SIMT) return LASP_ERR_PATH;
+  m->path = path;
+  m->chunk = (path == LASP_PATH_TENSOR) ? lasp::kTensorChunk : lasp::kSimtChunk;
+  m->nc = (p->n + m->chunk - 1) / m->chunk;
+  return LASP_OK;
+}
+
+size_t workspace_bytes(const lasp::Dims& m) {
+  size_t s = lasp::state_elems(m);
+  size_t bytes = s * 4;
+  if (m.path == LASP_PATH_TENSOR) bytes += s * 2;
+  return (bytes + 255) & ~(size_t)255;
+}
+
+int check_fwd(const lasp_problem* p, const lasp_fwd_args* a, lasp::Dims* m, bool need_qo) {
+  int st = make_dims(p, m);
+  if (st != LASP_OK) return st;
+  if (!a || !a->k || !a->v || !a->s || !a->ws) return LASP_ERR_NULL;
+  if (need_qo && (!a->q || !a->o)) return LASP_ERR_NULL;
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o) || !aligned16(a->kv_in) ||
+      !aligned16(a->kv_out) || !aligned16(a->ws))
+    return LASP_ERR_ALIGN;
+  if (a->ws_bytes < workspace_bytes(*m)) return LASP_ERR_WORKSPACE;
+  return LASP_OK;
+}
+
+int check_bwd(const lasp_problem* p, const lasp_bwd_args* a, lasp::Dims* m, bool need_all) {
+  int st = make_dims(p, m);
+  if (st != LASP_OK) return st;
+  if (!a || !a->q || !a->d_o || !a->s || !a->ws) return LASP_ERR_NULL;
+  if (need_all && (!a->k || !a->v || !a->dq || !a->dk || !a->dv || !a->fwd_ws)) return LASP_ERR_NULL;
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->d_o) || !aligned16(a->dq) ||
+      !aligned16(a->dk) || !aligned16(a->dv) || !aligned16(a->dkv_in) || !aligned16(a->dkv_out) ||
+      !aligned16(a->ws) || !aligned16(a->fwd_ws))
+    return LASP_ERR_ALIGN;
+  if (a->ws_bytes < workspace_bytes(*m)) return LASP_ERR_WORKSPACE;
+  if (need_all && a->fwd_ws_bytes < workspace_bytes(*m)) return LASP_ERR_WORKSPACE;
+  return LASP_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int lasp_b200_abi_version(void) { return LASP_B200_ABI_VERSION; }
+
+const char* lasp_b200_strerror(int status) {
+  switch (status) {
+    case LASP_OK: return "ok";
+    case LASP_ERR_NULL: return "a required pointer is NULL";
+    case LASP_ERR_SHAPE: return "unsupported shape (need b,h,n > 0; d,e multiples of 16 up to 128; b*h <= 65535)";
+    case LASP_ERR_DTYPE: return "unknown dtype";
+    case LASP_ERR_ALIGN: return "pointer not 16-byte aligned";
+    case LASP_ERR_WORKSPACE: return "workspace too small";
+    case LASP_ERR_CUDA: return "CUDA runtime error";
+    case LASP_ERR_PATH: return "requested kernel path cannot run this problem";
+    case LASP_ERR_DEVICE: return "a kernel reported a fault";
+    case LASP_ERR_TOO_LARGE: return "problem exceeds the fixed capacity of this entry point";
+    default: return "unknown status";
+  }
+}
+
+const char* lasp_b200_last_cuda_error(void) { return g_cuda_error; }
+
+int lasp_b200_resolve_path(const lasp_problem* p) {
+  lasp::Dims m;
+  int st = make_dims(p, &m);
+  return st != LASP_OK ? st : m.path;
+}
+
+int lasp_b200_chunk_tokens(const lasp_problem* p) {
+  lasp::Dims m;
+  int st = make_dims(p, &m);
+  return st != LASP_OK ? st : m.chunk;
+}
+
+size_t lasp_b200_fwd_workspace_bytes(const lasp_problem* p) {
+  lasp::Dims m;
+  return make_dims(p, &m) == LASP_OK ? workspace_bytes(m) : 0;
+}
+
+size_t lasp_b200_bwd_workspace_bytes(const lasp_problem* p) { return lasp_b200_fwd_workspace_bytes(p); }
+
+// ---- forward --------------------------------------------------------------
+int lasp_b200_fwd_chunk_states(const lasp_problem* p, const lasp_fwd_args* a, void* stream) {
+  lasp::Dims m;
+  int st = check_fwd(p, a, &m, false);
+  if (st != LASP_OK) return st;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (m.path == LASP_PATH_TENSOR)
+    return cuda_fail(lasp::tensor_chunk_states(m, a->k, a->v, a->s, lasp::ws_states_f32(a->ws), false, cs));
+  return cuda_fail(lasp::simt_chunk_states(m, a->k, a->v, a->s, lasp::ws_states_f32(a->ws), false, cs));
+}
+
+int lasp_b200_fwd_scan(const lasp_problem* p, const lasp_fwd_args* a, void* stream) {
+  lasp::Dims m;
+  int st = check_fwd(p, a, &m, false);
+  if (st != LASP_OK) return st;
+  __nv_bfloat16* bf = (m.path == LASP_PATH_TENSOR) ? lasp::ws_states_bf16(a->ws, m) : nullptr;
+  return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_states_f32(a->ws), bf, a->kv_in, a->kv_out, false,
+                                     static_cast<cudaStream_t>(stream)));
+}
+
+int lasp_b200_fwd_output(const lasp_problem* p, const lasp_fwd_args* a, void* stream) {
+  lasp::Dims m;
+  int st = check_fwd(p, a, &m, true);
+  if (st != LASP_OK) return st;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (m.path == LASP_PATH_TENSOR)
+    return cuda_fail(lasp::tensor_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_states_bf16(a->ws, m), a->o, cs));
+  return cuda_fail(lasp::simt_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_states_f32(a->ws), a->o, cs));
+}
+
+int lasp_b200_forward(const lasp_problem* p, const lasp_fwd_args* a, void* stream) {
+  lasp::Dims m;
+  int st = check_fwd(p, a, &m, true);
+  if (st != LASP_OK) return st;
+  if ((st = lasp_b200_fwd_chunk_states(p, a, stream)) != LASP_OK) return st;
+  if ((st = lasp_b200_fwd_scan(p, a, stream)) != LASP_OK) return st;
+  return lasp_b200_fwd_output(p, a, stream);
+}
+
+// ---- backward -------------------------------------------------------------
+int lasp_b200_bwd_chunk_states(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
+  lasp::Dims m;
+  int st = check_bwd(p, a, &m, false);
+  if (st != LASP_OK) return st;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (m.path == LASP_PATH_TENSOR)
+    return cuda_fail(lasp::tensor_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_states_f32(a->ws), true, cs));
+  return cuda_fail(lasp::simt_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_states_f32(a->ws), true, cs));
+}
+
+int lasp_b200_bwd_scan(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
+  lasp::Dims m;
+  int st = check_bwd(p, a, &m, false);
+  if (st != LASP_OK) return st;
+  __nv_bfloat16* bf = (m.path == LASP_PATH_TENSOR) ? lasp::ws_states_bf16(a->ws, m) : nullptr;
+  return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_states_f32(a->ws), bf, a->dkv_in, a->dkv_out, true,
+                                     static_cast<cudaStream_t>(stream)));
+}
+
+int lasp_b200_bwd_grads(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
+  lasp::Dims m;
+  int st = check_bwd(p, a, &m, true);
+  if (st != LASP_OK) return st;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (m.path == LASP_PATH_TENSOR)
+    return cuda_fail(lasp::tensor_bwd_grads(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_states_bf16(a->fwd_ws, m),
+                                            lasp::ws_states_bf16(a->ws, m), a->dq, a->dk, a->dv, cs));
+  return cuda_fail(lasp::simt_bwd_grads(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_states_f32(a->fwd_ws),
+                                        lasp::ws_states_f32(a->ws), a->dq, a->dk, a->dv, cs));
+}
+
+int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
+  lasp::Dims m;
+  int st = check_bwd(p, a, &m, true);
+  if (st != LASP_OK) return st;
+  if ((st = lasp_b200_bwd_chunk_states(p, a, stream)) != LASP_OK) return st;
+  if ((st = lasp_b200_bwd_scan(p, a, stream)) != LASP_OK) return st;
+  return lasp_b200_bwd_grads(p, a, stream);
+}
+
+int lasp_b200_state_combine(int b, int h, int d, int e, int n, const float* s, const float* x_in,
+                            const float* x_local, float* x_out, void* stream) {
+  if (!s || !x_local || !x_out) return LASP_ERR_NULL;
+  if (b <= 0 || h <= 0 || d <= 0 || e <= 0 || n < 0 || (d * e) % 4 || (long long)b * h > 65535) return LASP_ERR_SHAPE;
+  if (!aligned16(x_in) || !aligned16(x_local) || !aligned16(x_out)) return LASP_ERR_ALIGN;
+  return cuda_fail(lasp::state_combine(b, h, d, e, n, s, x_in, x_local, x_out, static_cast<cudaStream_t>(stream)));
+}
+
+int lasp_b200_read_status(int32_t* status_host, int clear, void* stream) {
+  if (!status_host) return LASP_ERR_NULL;
+  return cuda_fail(lasp::read_fault_word(status_host, clear != 0, static_cast<cudaStream_t>(stream)));
+}
+
+}  // extern "C"

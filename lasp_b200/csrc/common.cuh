@@ -1,0 +1,74 @@
+// Shared declarations of the lasp_b200 CUDA library (sm_100a).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "lasp_b200.h"
+
+namespace lasp {
+
+// Workspace layout (forward and backward use the same one):
+//   [0, S*4)                     fp32 chunk states, (b,h,nc,d,e); local states
+//                                after the chunk-state phase; on the SIMT path
+//                                the scan turns them into prefix states in place
+//   [.., .. + S*2)               TENSOR path only: bf16 prefix states written by
+//                                the scan, (b,h,nc,d,e) row-major (d rows, e cols)
+// with S = b*h*nc*d*e.
+constexpr int kSimtChunk = 64;     // the reference's block size
+constexpr int kTensorChunk = 128;  // one tcgen05 M=128 tile
+
+struct Dims {
+  int b, h, n, d, e;
+  int chunk;  // tokens per chunk state
+  int nc;     // chunks per sequence
+  int dtype;
+  int path;
+};
+
+inline size_t state_elems(const Dims& m) { return (size_t)m.b * m.h * m.nc * m.d * m.e; }
+
+inline float* ws_states_f32(void* ws) { return reinterpret_cast<float*>(static_cast<char*>(ws)); }
+inline const float* ws_states_f32(const void* ws) {
+  return reinterpret_cast<const float*>(static_cast<const char*>(ws));
+}
+inline __nv_bfloat16* ws_states_bf16(void* ws, const Dims& m) {
+  return reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + state_elems(m) * 4);
+}
+inline const __nv_bfloat16* ws_states_bf16(const void* ws, const Dims& m) {
+  return reinterpret_cast<const __nv_bfloat16*>(static_cast<const char*>(ws) + state_elems(m) * 4);
+}
+
+// bits of the sticky per-device fault word (tensor_kernels.cu owns the word)
+enum : int32_t {
+  kFaultNone = 0,
+  kFaultTmaWait = 1,   // a bounded wait on a TMA mbarrier ran out
+  kFaultMmaWait = 2,   // a bounded wait on a tcgen05.commit mbarrier ran out
+};
+cudaError_t read_fault_word(int32_t* host, bool clear, cudaStream_t st);
+
+// ---- launchers implemented in the .cu files (return cudaError_t) -----------
+cudaError_t simt_chunk_states(const Dims& m, const void* a, const void* bten, const float* s, float* states,
+                              bool backward, cudaStream_t st);
+cudaError_t scan_states(const Dims& m, const float* s, float* states, __nv_bfloat16* states_bf16,
+                        const float* x_in, float* x_out, bool reverse, cudaStream_t st);
+cudaError_t simt_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
+                            const float* prefix, void* o, cudaStream_t st);
+cudaError_t simt_bwd_grads(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
+                           const float* s, const float* prefix, const float* suffix, void* dq, void* dk,
+                           void* dv, cudaStream_t st);
+cudaError_t state_combine(int b, int h, int d, int e, int n, const float* s, const float* x_in,
+                          const float* x_local, float* x_out, cudaStream_t st);
+
+// tcgen05 path (tensor_kernels.cu)
+cudaError_t tensor_chunk_states(const Dims& m, const void* a, const void* bten, const float* s, float* states,
+                                bool backward, cudaStream_t st);
+cudaError_t tensor_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
+                              const __nv_bfloat16* prefix, void* o, cudaStream_t st);
+cudaError_t tensor_bwd_grads(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
+                             const float* s, const __nv_bfloat16* prefix, const __nv_bfloat16* suffix, void* dq,
+                             void* dk, void* dv, cudaStream_t st);
+bool tensor_path_supported(const Dims& m);
+
+}  // namespace lasp

@@ -1,0 +1,164 @@
+"""Torch-facing launcher of the C-ABI kernels.
+
+Takes contiguous CUDA tensors, fills the ``lasp_problem`` / ``lasp_fwd_args`` /
+``lasp_bwd_args`` structures of include/lasp_b200.h and calls the library on
+torch's current stream.  PyTorch is used for device memory and streams only.
+
+This module is what the five operators call; it plays the role of the
+reference's launchers ``lasp_forward`` / ``lasp_backward``
+(lasp/lasp_fuse_parallel.py:833-944, 947-1070).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+
+import torch
+
+from . import _cabi
+
+_DTYPES = {torch.float32: _cabi.F32, torch.bfloat16: _cabi.BF16, torch.float16: _cabi.F16}
+_PATHS = {"auto": _cabi.PATH_AUTO, "simt": _cabi.PATH_SIMT, "tensor": _cabi.PATH_TENSOR}
+
+
+def default_path() -> str:
+    """Kernel path used when an operator is not told one: env LASP_B200_PATH or 'auto'."""
+    return os.environ.get("LASP_B200_PATH", "auto")
+
+
+@dataclass
+class Plan:
+    """A validated problem: shape, dtype, resolved kernel path, workspace size."""
+    problem: _cabi.Problem
+    b: int
+    h: int
+    n: int
+    d: int
+    e: int
+    path: int           # _cabi.PATH_SIMT or _cabi.PATH_TENSOR
+    chunk: int          # tokens per chunk state
+    ws_bytes: int
+
+    @property
+    def path_name(self) -> str:
+        return "tensor" if self.path == _cabi.PATH_TENSOR else "simt"
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("lasp_b200 runs on CUDA tensors only (there is no CPU fallback); "
+                               f"got a tensor on {t.device}")
+
+
+def make_plan(b: int, h: int, n: int, d: int, e: int, dtype: torch.dtype, path: str | None = None) -> Plan:
+    if dtype not in _DTYPES:
+        raise TypeError(f"unsupported dtype {dtype}; use float32, bfloat16 or float16")
+    name = path or default_path()
+    if name not in _PATHS:
+        raise ValueError(f"unknown kernel path {name!r}; use auto, simt or tensor")
+    prob = _cabi.Problem(b, h, n, d, e, _DTYPES[dtype], _PATHS[name], 0)
+    resolved = _cabi.call("lasp_b200_resolve_path", C.byref(prob))
+    prob.path = resolved
+    chunk = _cabi.call("lasp_b200_chunk_tokens", C.byref(prob))
+    ws = _cabi.load().lasp_b200_fwd_workspace_bytes(C.byref(prob))
+    return Plan(prob, b, h, n, d, e, resolved, chunk, ws)
+
+
+def new_workspace(plan: Plan, device) -> torch.Tensor:
+    return torch.empty(plan.ws_bytes, dtype=torch.uint8, device=device)
+
+
+def _slopes(s: torch.Tensor, h: int, device) -> torch.Tensor:
+    s = s.reshape(-1)
+    if s.numel() != h:
+        raise ValueError(f"decay tensor has {s.numel()} entries for {h} heads")
+    return s.to(device=device, dtype=torch.float32).contiguous()
+
+
+class Forward:
+    """One forward call split in its three phases (see include/lasp_b200.h)."""
+
+    def __init__(self, plan: Plan, q, k, v, s, kv_in=None, kv_out=None, o=None, ws=None):
+        _require_cuda(q, k, v, kv_in, kv_out)
+        self.plan = plan
+        self.q, self.k, self.v = q, k, v
+        self.s = _slopes(s, plan.h, q.device)
+        self.kv_in, self.kv_out = kv_in, kv_out
+        self.o = o if o is not None else torch.empty(plan.b, plan.h, plan.n, plan.e, dtype=q.dtype, device=q.device)
+        self.ws = ws if ws is not None else new_workspace(plan, q.device)
+        self._args = _cabi.FwdArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(self.s), _ptr(kv_in), _ptr(kv_out),
+                                   _ptr(self.o), _ptr(self.ws), self.ws.numel())
+
+    def _call(self, fn):
+        _cabi.call(fn, C.byref(self.plan.problem), C.byref(self._args), _stream())
+
+    def chunk_states(self):
+        self._call("lasp_b200_fwd_chunk_states")
+
+    def scan(self):
+        self._call("lasp_b200_fwd_scan")
+
+    def output(self):
+        self._call("lasp_b200_fwd_output")
+
+    def run(self):
+        self._call("lasp_b200_forward")
+        return self.o
+
+
+class Backward:
+    """One backward call split in its three phases."""
+
+    def __init__(self, plan: Plan, q, k, v, do, s, fwd_ws, dkv_in=None, dkv_out=None, ws=None):
+        _require_cuda(q, k, v, do, fwd_ws, dkv_in, dkv_out)
+        self.plan = plan
+        self.s = _slopes(s, plan.h, q.device)
+        self.keep = (q, k, v, do, fwd_ws, dkv_in, dkv_out)
+        self.dq, self.dk, self.dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        self.ws = ws if ws is not None else new_workspace(plan, q.device)
+        self._args = _cabi.BwdArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(do), _ptr(self.s), _ptr(dkv_in), _ptr(dkv_out),
+                                   _ptr(self.dq), _ptr(self.dk), _ptr(self.dv), _ptr(fwd_ws), fwd_ws.numel(),
+                                   _ptr(self.ws), self.ws.numel())
+
+    def _call(self, fn):
+        _cabi.call(fn, C.byref(self.plan.problem), C.byref(self._args), _stream())
+
+    def chunk_states(self):
+        self._call("lasp_b200_bwd_chunk_states")
+
+    def scan(self):
+        self._call("lasp_b200_bwd_scan")
+
+    def grads(self):
+        self._call("lasp_b200_bwd_grads")
+
+    def run(self):
+        self._call("lasp_b200_backward")
+        return self.dq, self.dk, self.dv
+
+
+def state_combine(s, x_in, x_local, n: int, out=None):
+    """out = exp(-s n) x_in + x_local on (b,h,d,e) fp32 states."""
+    _require_cuda(x_local, x_in)
+    b, h, d, e = x_local.shape
+    out = out if out is not None else torch.empty_like(x_local)
+    _cabi.call("lasp_b200_state_combine", b, h, d, e, n, _ptr(_slopes(s, h, x_local.device)), _ptr(x_in),
+               _ptr(x_local), _ptr(out), _stream())
+    return out
+
+
+def read_status(clear: bool = True) -> int:
+    """Sticky kernel-fault word of the current device (synchronises)."""
+    word = C.c_int32(0)
+    _cabi.call("lasp_b200_read_status", C.byref(word), 1 if clear else 0, _stream())
+    return word.value
