@@ -1,0 +1,322 @@
+"""Benchmark of the LASP linear-attention hot path (forward + backward).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload: BASELINE config 1 - per rank b=2, h=12, 2048 tokens, d=e=128, bf16,
+seeded synthetic N(0,1) inputs (q,k scaled by d^-0.5), slopes 2^(-8(i+1)/12).
+With N GPUs the N ranks form one sequence-parallel group (DP=1, SP=N; global
+sequence 2048*N) unless --dp says otherwise; per-rank work is fixed (weak
+scaling).  A step is one forward + one backward of the operator.
+
+One JSON line is printed by rank 0:
+  value  - tokens/s with inputs resident in HBM (device-timed, max over ranks);
+           the inputs rotate over enough independent sets to exceed the L2;
+  e2e    - tokens/s through the public operator with pinned HOST buffers:
+           host->device copies of q,k,v,do and device->host copies of
+           o,dq,dk,dv are inside the timed region;
+  roofline     - the dominant kernel (backward gradients) against measured HBM peak;
+  cpu_baseline - the CPU oracle (a port of the reference's arithmetic; the
+           reference has no CPU implementation) on this box's host cores.
+
+--impl reference times that CPU port alone, with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+# BASELINE config 1, per rank
+B, H, N_LOCAL, D, E = 2, 12, 2048, 128, 128
+METRIC = "fwd+bwd tokens/s, LASP linear attention (b=2/rank, h=12, 2048 tokens/rank, d=e=128)"
+UNIT = "tokens/s"
+FALLBACK_HBM_GBS = 6650.0
+L2_BYTES = 126e6
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
+# from the ncu capture summarised under profiles/ (None until one exists)
+DOMINANT_KERNEL_TRAFFIC_BYTES = None
+
+
+def env_int(name, default):
+    return int(os.environ.get(name, default))
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p["bf16_tflops_sustained"]), "measured"
+    except Exception:  # noqa: BLE001
+        return FALLBACK_HBM_GBS, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while a region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.06)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i] == "Active"})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def slopes(h):
+    i = torch.arange(1, h + 1, dtype=torch.float64)
+    return torch.pow(2.0, -8.0 * i / h).float().reshape(h, 1, 1)
+
+
+def make_set(seed, device, dtype, pinned=False):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, H, N_LOCAL, D, generator=g) * D ** -0.5
+    k = torch.randn(B, H, N_LOCAL, D, generator=g) * D ** -0.5
+    v = torch.randn(B, H, N_LOCAL, E, generator=g)
+    do = torch.randn(B, H, N_LOCAL, E, generator=g)
+    ts = [t.to(dtype) for t in (q, k, v, do)]
+    if pinned:
+        return [t.pin_memory() for t in ts]
+    return [t.to(device) for t in ts]
+
+
+# ---------------------------------------------------------------------------
+# reference arm / cpu baseline: the oracle on the host cores
+# ---------------------------------------------------------------------------
+def cpu_port_tokens_per_s(reps, warm=1):
+    from oracle import lasp_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    q, k, v, do = O.make_inputs(0, B, H, N_LOCAL, D, E)
+    s = O.baseline_slopes(H)
+    for _ in range(warm):
+        O.fwd_bwd(q, k, v, s, do)
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        O.fwd_bwd(q, k, v, s, do)
+        times.append(time.perf_counter() - t0)
+    return B * N_LOCAL / statistics.median(times), torch.get_num_threads(), times
+
+
+def run_reference(args):
+    rank = env_int("RANK", 0)
+    if rank != 0:
+        return
+    value, cores, times = cpu_port_tokens_per_s(args.steps, max(1, min(args.warmup, 2)))
+    sample = (f"each step = one rank's chunk (b={B},h={H},n={N_LOCAL},d=e={D}) in fp32, blocked (B=64) torch port "
+              f"of the reference's kernels; {args.steps} steps, median")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * statistics.median(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "BASELINE config 1 per-rank chunk on CPU", "b": B, "h": H, "n": N_LOCAL, "d": D,
+                   "e": E},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+def run_ours(args):
+    import torch.distributed as dist
+    from lasp_b200 import engine, lasp_fuse_parallel, lightning_attn
+    from lasp_b200.utils import initialize_lasp
+
+    rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    dp = args.dp
+    sp = world // dp
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        initialize_lasp(dp, sp)
+    dtype = torch.bfloat16
+    s = slopes(H).to(device)
+
+    # enough independent input sets that a step never finds its inputs in L2
+    set_bytes = (2 * D + 2 * E) * 2 * B * H * N_LOCAL
+    n_sets = max(2, int(L2_BYTES * 1.6 // set_bytes) + 1)
+    sets = [make_set(1000 * rank + i, device, dtype) for i in range(n_sets)]
+    for st in sets:
+        for t in st[:3]:
+            t.requires_grad_(True)
+    KV = torch.empty(B, H, D, E, device=device)
+    DKV = torch.empty(B, H, D, E, device=device)
+
+    def step(i):
+        q, k, v, do = sets[i % n_sets]
+        q.grad = k.grad = v.grad = None
+        if sp > 1:
+            o = lasp_fuse_parallel(q, k, v, s, KV, DKV)
+        else:
+            o = lightning_attn(q, k, v, s)
+        o.backward(do)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    sync_all()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        sync_all()
+        start.record()
+        for i in range(args.steps):
+            step(args.warmup + i)
+        stop.record()
+        sync_all()
+    ms = torch.tensor([start.elapsed_time(stop)], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = ms.item() / args.steps
+    tokens_per_step = B * dp * N_LOCAL * sp
+    value = tokens_per_step / (ms_per_step * 1e-3)
+
+    # ---- end to end through the public operator with host buffers ---------
+    host_in = make_set(5000 + rank, device, dtype, pinned=True)
+    host_out = [torch.empty_like(t).pin_memory() for t in host_in]
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+
+    def e2e_step():
+        q, k, v, do = (t.to(device, non_blocking=True) for t in host_in)
+        q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+        o = lasp_fuse_parallel(q, k, v, s, KV, DKV) if sp > 1 else lightning_attn(q, k, v, s)
+        o.backward(do)
+        for dst, src in zip(host_out, (o.detach(), q.grad, k.grad, v.grad)):
+            dst.copy_(src, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(3):
+        e2e_step()
+    sync_all()
+    start.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    stop.record()
+    sync_all()
+    ms2 = torch.tensor([start.elapsed_time(stop)], device=device)
+    if world > 1:
+        dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
+    e2e_value = tokens_per_step / (ms2.item() / e2e_steps * 1e-3)
+
+    # ---- dominant kernel alone: backward gradients --------------------------
+    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+    plan = engine.make_plan(B, H, N_LOCAL, D, E, dtype)
+    fws, bws = [], []
+    for q, k, v, do in sets:
+        fw = engine.Forward(plan, q.detach(), k.detach(), v.detach(), s)
+        fw.run()
+        bw = engine.Backward(plan, q.detach(), k.detach(), v.detach(), do, s, fw.ws)
+        bw.chunk_states(), bw.scan()
+        fws.append(fw), bws.append(bw)
+    for bw in bws:
+        bw.grads()
+    torch.cuda.synchronize()
+    reps = max(20, 2 * n_sets)
+    start.record()
+    for i in range(reps):
+        bws[i % n_sets].grads()
+    stop.record()
+    torch.cuda.synchronize()
+    kernel_ms = start.elapsed_time(stop) / reps
+    kernel_bytes = (4 * D + 3 * E) * 2 * B * H * N_LOCAL      # reads q,k,v,do; writes dq,dk,dv
+    achieved = kernel_bytes / (kernel_ms * 1e-3) / 1e9
+    step_bytes = (6 * D + 5 * E) * 2 * B * H * N_LOCAL
+    step_flops = (2 * 64 * (4 * D + 3 * E) + 12 * D * E) * B * H * N_LOCAL
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+    cpu_value, cores, _ = cpu_port_tokens_per_s(3)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "BASELINE config 1: lightning attention fwd+bwd, b=2/rank, h=12, 2048 tokens/rank, "
+                               "d=e=128, decay 2^(-8(i+1)/12)", "parallelism": f"dp{dp}xsp{sp}",
+                   "global_batch": B * dp, "global_seq_len": N_LOCAL * sp, "kernel_path": plan.path_name,
+                   "l2": f"inputs rotate over {n_sets} independent sets ({n_sets * set_bytes / 1e6:.0f} MB) > L2"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps},
+        "gpu_launches": 6 * args.steps,
+        "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "kernel": f"bwd_grads ({plan.path_name})", "achieved": achieved,
+                     "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_kind,
+                     "traffic": DOMINANT_KERNEL_TRAFFIC_BYTES, "kernel_ms": kernel_ms,
+                     "algorithmic_bytes_per_launch": kernel_bytes,
+                     "step_hbm_frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak,
+                     "step_tensor_frac": step_flops / (ms_per_step * 1e-3) / 1e12 / tensor_peak},
+        "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"3 runs of one rank's chunk (b={B},h={H},n={N_LOCAL},d=e={D}) fp32, median"},
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--dp", type=int, default=1, help="data-parallel size; sequence-parallel size = gpus / dp")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,203 @@
+"""GPU parity: the CUDA path (through the ctypes C ABI) against the reference's
+golden outputs and against the CPU oracle on seeded inputs.
+
+Gates (max|x - ref| / max|ref|): 1e-3 for fp32 I/O, 2e-2 for bf16/fp16 I/O with
+fp32 accumulation.
+"""
+import pytest
+import torch
+
+from oracle import lasp_oracle as O
+from tests.helpers import CASES, TOL_BF16, TOL_FP32, case_inputs, golden_tensor, load_golden
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _tol(dtype):
+    return TOL_FP32 if dtype == torch.float32 else TOL_BF16
+
+
+def run_lightning(q, k, v, do, s, dtype, path=None, monkeypatch=None):
+    from lasp_b200 import lightning_attn
+    if path and monkeypatch:
+        monkeypatch.setenv("LASP_B200_PATH", path)
+    qd, kd, vd, dod = (t.to(DEV, dtype) for t in (q, k, v, do))
+    qd.requires_grad_(True), kd.requires_grad_(True), vd.requires_grad_(True)
+    o = lightning_attn(qd, kd, vd, s.to(DEV))
+    o.backward(dod)
+    torch.cuda.synchronize()
+    return o.detach(), qd.grad, kd.grad, vd.grad
+
+
+def oracle_on_rounded(q, k, v, do, s, dtype):
+    """oracle in fp64-accurate fp32 on the inputs as the device sees them"""
+    r = [t.to(dtype).float() for t in (q, k, v, do)]
+    return O.fwd_bwd(r[0], r[1], r[2], s, r[3])
+
+
+@pytest.mark.parametrize("name", sorted(CASES["single"]))
+def test_lightning_attn_matches_reference_golden(name):
+    p = CASES["single"][name]
+    q, k, v, do, s = case_inputs(p)
+    got = run_lightning(q, k, v, do, s, torch.float32)
+    g = load_golden(name)
+    for t, key in zip(got, ("o", "dq", "dk", "dv")):
+        assert t.shape == g[key].shape
+        assert O.max_rel_err(t, golden_tensor(g[key])) < TOL_FP32, key
+
+
+SHAPES = [
+    # b, h, n, d, e
+    (1, 1, 64, 16, 16),      # one block, smallest head dims
+    (2, 3, 128, 64, 64),
+    (1, 2, 65, 32, 48),      # ragged: one token into the second block
+    (1, 2, 1, 64, 64),       # a single token
+    (2, 2, 333, 128, 64),    # the reference test's d=128, e=64, ragged n
+    (1, 4, 1024, 128, 128),
+    (1, 2, 512, 96, 112),    # multiples of 16 that are not powers of two
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_fp32_kernels_against_oracle(shape, dtype, monkeypatch):
+    b, h, n, d, e = shape
+    q, k, v, do = O.make_inputs(100 + n, b, h, n, d, e)
+    s = O.baseline_slopes(h)
+    got = run_lightning(q, k, v, do, s, dtype, "simt", monkeypatch)
+    ref = oracle_on_rounded(q, k, v, do, s, dtype)
+    for t, r, key in zip(got, ref, ("o", "dq", "dk", "dv")):
+        assert t.dtype == dtype
+        assert O.max_rel_err(t, r) < _tol(dtype), (key, shape)
+
+
+def test_wide_heads_are_sliced(monkeypatch):
+    # d = 256 (two q/k slices summed) and e = 192 (two v slices concatenated)
+    q, k, v, do = O.make_inputs(5, 1, 2, 256, 256, 192)
+    s = O.baseline_slopes(2)
+    got = run_lightning(q, k, v, do, s, torch.float32)
+    ref = O.dense_closed_form(q, k, v, s, do)
+    for t, r in zip(got, ref):
+        assert O.max_rel_err(t, r) < TOL_FP32
+
+
+def test_no_decay_feature_map():
+    # LinearTransformer-style config: s = 0, elu(x)+1 on q and k, no 1/sqrt(d)
+    q, k, v, do = O.make_inputs(6, 2, 2, 512, 64, 64, scale_qk=False, feature_map="elu1")
+    s = torch.zeros(2, 1, 1)
+    got = run_lightning(q, k, v, do, s, torch.float32)
+    ref = O.fwd_bwd(q, k, v, s, do, dtype=torch.float64)
+    for t, r in zip(got, ref):
+        assert O.max_rel_err(t, r) < TOL_FP32
+
+
+def test_baseline_config0_full_size_fp32():
+    # b=2, n=2048, h=12, d=e=128, fp32: the reference's CPU-runnable configuration
+    q, k, v, do = O.make_inputs(0, 2, 12, 2048, 128, 128)
+    s = O.baseline_slopes(12)
+    got = run_lightning(q, k, v, do, s, torch.float32)
+    ref = O.fwd_bwd(q, k, v, s, do)
+    for t, r, key in zip(got, ref, ("o", "dq", "dk", "dv")):
+        assert O.max_rel_err(t, r) < TOL_FP32, key
+
+
+def _chain_on_one_gpu(q, k, v, do, s, sp, dtype, path):
+    """Emulate `sp` sequence-parallel ranks one after another on one device by
+    threading kv/dkv states through the C-ABI calls."""
+    from lasp_b200 import engine
+    b, h, n, d = q.shape
+    e = v.shape[-1]
+    nl = n // sp
+    sd = s.to(DEV)
+    parts = [[t[:, :, r * nl:(r + 1) * nl].to(DEV, dtype).contiguous() for r in range(sp)] for t in (q, k, v, do)]
+    plan = engine.make_plan(b, h, nl, d, e, dtype, path)
+    KV = torch.full((b, h, d, e), float("nan"), device=DEV)
+    fws, outs = [], []
+    for r in range(sp):
+        fw = engine.Forward(plan, parts[0][r], parts[1][r], parts[2][r], sd, kv_in=KV if r > 0 else None,
+                            kv_out=KV if r < sp - 1 else None)
+        outs.append(fw.run())
+        fws.append(fw)
+    DKV = torch.full((b, h, d, e), float("nan"), device=DEV)
+    grads = [None] * sp
+    for r in reversed(range(sp)):
+        bw = engine.Backward(plan, parts[0][r], parts[1][r], parts[2][r], parts[3][r], sd, fws[r].ws,
+                             dkv_in=DKV if r < sp - 1 else None, dkv_out=DKV if r > 0 else None)
+        grads[r] = bw.run()
+    torch.cuda.synchronize()
+    o = torch.cat(outs, 2)
+    dq, dk, dv = (torch.cat([g[i] for g in grads], 2) for i in range(3))
+    return o, dq, dk, dv
+
+
+@pytest.mark.parametrize("sp", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rank_chain_equals_single_device(sp, dtype):
+    q, k, v, do = O.make_inputs(20 + sp, 2, 3, 64 * 2 * sp, 64, 32)
+    s = O.baseline_slopes(3)
+    got = _chain_on_one_gpu(q, k, v, do, s, sp, dtype, "simt")
+    ref = oracle_on_rounded(q, k, v, do, s, dtype)
+    for t, r, key in zip(got, ref, ("o", "dq", "dk", "dv")):
+        assert O.max_rel_err(t, r) < _tol(dtype), (key, sp)
+
+
+def test_state_combine_and_outgoing_states():
+    from lasp_b200 import engine
+    b, h, n, d, e = 2, 3, 200, 32, 48
+    q, k, v, do = O.make_inputs(31, b, h, n, d, e)
+    s = O.baseline_slopes(h)
+    kv_in = torch.randn(b, h, d, e)
+    dkv_in = torch.randn(b, h, d, e)
+    _, kv_ref = O.blocked_forward(q, k, v, s, kv_in)
+    *_, dkv_ref = O.blocked_backward(q, k, v, s, do, kv_in, dkv_in)
+    plan = engine.make_plan(b, h, n, d, e, torch.float32, "simt")
+    dev = [t.to(DEV) for t in (q, k, v, do)]
+    kv_out = torch.empty(b, h, d, e, device=DEV)
+    dkv_out = torch.empty(b, h, d, e, device=DEV)
+    fw = engine.Forward(plan, dev[0], dev[1], dev[2], s.to(DEV), kv_in=kv_in.to(DEV), kv_out=kv_out)
+    fw.run()
+    bw = engine.Backward(plan, dev[0], dev[1], dev[2], dev[3], s.to(DEV), fw.ws, dkv_in=dkv_in.to(DEV),
+                         dkv_out=dkv_out)
+    bw.run()
+    assert O.max_rel_err(kv_out, kv_ref) < 1e-5
+    assert O.max_rel_err(dkv_out, dkv_ref) < 1e-5
+    x_local = torch.randn(b, h, d, e)
+    got = engine.state_combine(s.to(DEV), kv_in.to(DEV), x_local.to(DEV), n)
+    ref = torch.exp(-s.reshape(1, h, 1, 1) * n) * kv_in + x_local
+    assert O.max_rel_err(got, ref) < 1e-6
+    assert engine.read_status() == 0
+
+
+def test_linearity_and_split_property_at_long_sequence():
+    # size-independent properties at a TNL-1B-like layer slice: n = 32768 per head
+    from lasp_b200 import lightning_attn
+    b, h, n, d, e = 1, 2, 32768, 128, 128
+    g = torch.Generator(device=DEV).manual_seed(3)
+    q = torch.randn(b, h, n, d, device=DEV, generator=g) * d ** -0.5
+    k = torch.randn(b, h, n, d, device=DEV, generator=g) * d ** -0.5
+    v1 = torch.randn(b, h, n, e, device=DEV, generator=g)
+    v2 = torch.randn(b, h, n, e, device=DEV, generator=g)
+    s = O.baseline_slopes(16)[[0, 15]].to(DEV)
+    o1, o2 = lightning_attn(q, k, v1, s), lightning_attn(q, k, v2, s)
+    o12 = lightning_attn(q, k, 2.0 * v1 - 0.5 * v2, s)
+    assert O.max_rel_err(o12, 2.0 * o1 - 0.5 * o2) < 1e-4
+    # two halves chained through the rank state == the whole sequence
+    do = torch.randn(b, h, n, e, device=DEV, generator=g)
+    whole = _chain_on_one_gpu(q.cpu(), k.cpu(), v1.cpu(), do.cpu(), s.cpu(), 1, torch.float32, "simt")
+    halves = _chain_on_one_gpu(q.cpu(), k.cpu(), v1.cpu(), do.cpu(), s.cpu(), 2, torch.float32, "simt")
+    for a, bb in zip(whole, halves):
+        assert O.max_rel_err(a, bb) < 1e-4
+
+
+def test_errors_are_raised_not_swallowed():
+    from lasp_b200 import _cabi, lightning_attn
+    q = torch.randn(1, 1, 64, 24, device=DEV)       # d not a multiple of 16
+    with pytest.raises(_cabi.LaspStatusError):
+        lightning_attn(q, q, q, torch.zeros(1, 1, 1, device=DEV))
+    q = torch.randn(1, 2, 64, 32, device=DEV)
+    with pytest.raises(ValueError):
+        lightning_attn(q, q, q, torch.zeros(3, 1, 1, device=DEV))   # wrong head count
+    with pytest.raises(TypeError):
+        lightning_attn(q.double(), q.double(), q.double(), torch.zeros(2, 1, 1, device=DEV))
