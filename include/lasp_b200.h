@@ -160,6 +160,30 @@ int lasp_b200_state_combine(int b, int h, int d, int e, int n, const float* s, c
  * arrival, tcgen05 completion) runs out instead of spinning for ever. */
 int lasp_b200_read_status(int32_t* status_host, int clear, void* stream);
 
+/* Forward pass that allocates nothing and needs no workspace from the caller.
+ * (No counterpart in the reference, whose launchers allocate with torch.)
+ *
+ * For hosts that cannot allocate device memory when they call the operator:
+ * a server that gave the whole GPU to its own pool at start-up, or a serving
+ * loop in which cudaMalloc / cudaFree (they may synchronise the device) are
+ * off limits.  The chunk-state workspace is a fixed array inside the library,
+ * LASP_B200_STATIC_SCRATCH_BYTES on every GPU that loads the library, held
+ * until the process exits.  a->ws and a->ws_bytes are ignored; inputs, outputs
+ * and the optional rank states are the caller's, as in lasp_b200_forward, and
+ * the result is the same.
+ *   - Problems whose forward workspace (lasp_b200_fwd_workspace_bytes) is
+ *     larger than the array are refused with LASP_ERR_TOO_LARGE.
+ *   - The first call on each device looks up the array's device address (with
+ *     that device current); make that first call before any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents;
+ *     each call overwrites everything it later reads, so no clearing is needed,
+ *     but two calls whose kernels overlap on the GPU (different streams,
+ *     different threads) race - serialise them.
+ *   - The prefix states are not kept for a backward pass: this is a
+ *     forward-only (inference / prefill) entry point. */
+#define LASP_B200_STATIC_SCRATCH_BYTES (64u << 20)
+int lasp_b200_forward_static(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -69,7 +69,9 @@ SIGNATURES = {
     "lasp_b200_backward": (C.c_int, [_PP, _BP, C.c_void_p]),
     "lasp_b200_state_combine": (C.c_int, [C.c_int] * 5 + [C.c_void_p] * 5),
     "lasp_b200_read_status": (C.c_int, [C.POINTER(C.c_int32), C.c_int, C.c_void_p]),
+    "lasp_b200_forward_static": (C.c_int, [_PP, _FP, C.c_void_p]),
 }
+STATIC_SCRATCH_BYTES = 64 << 20  # LASP_B200_STATIC_SCRATCH_BYTES
 
 _lib = None
 
