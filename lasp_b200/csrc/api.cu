@@ -1,8 +1,13 @@
 // extern "C" entry points of liblasp_b200.so: argument validation, workspace
 // layout and the choice between the tensor-core and the fp32 kernels.
+#include <stdio.h>
 #include <string.h>
 
 #include "common.cuh"
+
+namespace lasp {
+thread_local const char* g_failed_step = "";
+}
 
 namespace {
 
@@ -10,9 +15,22 @@ thread_local char g_cuda_error[256] = "";
 
 int cuda_fail(cudaError_t err) {
   if (err == cudaSuccess) return LASP_OK;
-  strncpy(g_cuda_error, cudaGetErrorString(err), sizeof(g_cuda_error) - 1);
-  g_cuda_error[sizeof(g_cuda_error) - 1] = 0;
+  snprintf(g_cuda_error, sizeof(g_cuda_error), "%s%s%s", cudaGetErrorString(err),
+           lasp::g_failed_step[0] ? " in " : "", lasp::g_failed_step);
+  lasp::g_failed_step = "";
   return LASP_ERR_CUDA;
+}
+
+// A thread that has made no CUDA runtime call yet (PyTorch's autograd worker for
+// device 0 is one) has no driver context bound, and the driver-API tensor-map
+// encoder then fails.  The first entry on each thread binds the context of the
+// thread's current device.
+void bind_context_once() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -20,6 +38,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // validates the problem and fills Dims; returns LASP_OK or a negative status
 int make_dims(const lasp_problem* p, lasp::Dims* m) {
   if (!p) return LASP_ERR_NULL;
+  bind_context_once();
   if (p->dtype != LASP_F32 && p->dtype != LASP_BF16 && p->dtype != LASP_F16) return LASP_ERR_DTYPE;
   if (p->b <= 0 || p->h <= 0 || p->n <= 0 || p->d <= 0 || p->e <= 0) return LASP_ERR_SHAPE;
   if (p->d % 16 || p->e % 16 || p->d > 128 || p->e > 128) return LASP_ERR_SHAPE;

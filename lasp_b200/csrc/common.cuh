@@ -48,6 +48,9 @@ enum : int32_t {
 };
 cudaError_t read_fault_word(int32_t* host, bool clear, cudaStream_t st);
 
+// name of the host-side step that produced the last cudaError_t (for error text)
+extern thread_local const char* g_failed_step;
+
 // ---- launchers implemented in the .cu files (return cudaError_t) -----------
 cudaError_t simt_chunk_states(const Dims& m, const void* a, const void* bten, const float* s, float* states,
                               bool backward, cudaStream_t st);

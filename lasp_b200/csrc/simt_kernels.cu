@@ -87,8 +87,9 @@ __global__ void __launch_bounds__(NT) k_chunk_states(const T* __restrict__ A, co
 
 // ---------------------------------------------------------------------------
 // scan over chunks, elementwise in (d,e).  forward: exclusive prefix seeded
-// with x_in; reverse: exclusive suffix.  Writes prefix states in place (fp32)
-// and, when out_bf16 != nullptr, as bf16 (the tensor-core operand copy).
+// with x_in; reverse: exclusive suffix.  Writes the prefix states in place
+// (fp32) or, when out_bf16 != nullptr, as bf16 into that buffer instead (the
+// tensor-core operand copy; the fp32 local states are then left untouched).
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_scan(const float* __restrict__ s, float* __restrict__ states,
                                               __nv_bfloat16* __restrict__ out_bf16, const float* __restrict__ x_in,
@@ -109,8 +110,9 @@ __global__ void __launch_bounds__(256) k_scan(const float* __restrict__ s, float
     const int c = reverse ? nc - 1 - i : i;
     const float dec = (c == nc - 1) ? tail : full;
     float4 loc = *reinterpret_cast<const float4*>(base + (size_t)c * de);
-    *reinterpret_cast<float4*>(base + (size_t)c * de) = p;
-    if (bbase) {
+    if (!bbase) {
+      *reinterpret_cast<float4*>(base + (size_t)c * de) = p;
+    } else {
       __nv_bfloat162 lo = __floats2bfloat162_rn(p.x, p.y), hi = __floats2bfloat162_rn(p.z, p.w);
       uint2 pk;
       pk.x = *reinterpret_cast<uint32_t*>(&lo);

@@ -200,6 +200,12 @@ inline EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// CUresult of the last failed encode on this thread (diagnostics)
+inline int& last_encode_result() {
+  static thread_local int r = 0;
+  return r;
+}
+
 inline cudaError_t make_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uint32_t width,
                                  uint32_t box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
@@ -212,6 +218,7 @@ inline cudaError_t make_tile_map(CUtensorMap* map, const void* base, uint64_t ro
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) last_encode_result() = (int)r;
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 

@@ -53,6 +53,23 @@ def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class _on_device:
+    """Make ``device`` current for the duration of a library call.  Backward
+    runs on autograd's worker threads, whose current device need not be the
+    tensors' device; the library launches on the calling thread's device."""
+
+    def __init__(self, device):
+        self.idx = device.index if device.index is not None else torch.cuda.current_device()
+        self.prev = -1
+
+    def __enter__(self):
+        self.prev = torch.cuda._exchange_device(self.idx)
+
+    def __exit__(self, *exc):
+        torch.cuda._maybe_exchange_device(self.prev)
+        return False
+
+
 def _require_cuda(*ts):
     for t in ts:
         if t is not None and not t.is_cuda:
@@ -100,7 +117,8 @@ class Forward:
                                    _ptr(self.o), _ptr(self.ws), self.ws.numel())
 
     def _call(self, fn):
-        _cabi.call(fn, C.byref(self.plan.problem), C.byref(self._args), _stream())
+        with _on_device(self.q.device):
+            _cabi.call(fn, C.byref(self.plan.problem), C.byref(self._args), _stream())
 
     def chunk_states(self):
         self._call("lasp_b200_fwd_chunk_states")
@@ -131,7 +149,8 @@ class Backward:
                                    _ptr(self.ws), self.ws.numel())
 
     def _call(self, fn):
-        _cabi.call(fn, C.byref(self.plan.problem), C.byref(self._args), _stream())
+        with _on_device(self.keep[0].device):
+            _cabi.call(fn, C.byref(self.plan.problem), C.byref(self._args), _stream())
 
     def chunk_states(self):
         self._call("lasp_b200_bwd_chunk_states")

@@ -201,3 +201,65 @@ def test_errors_are_raised_not_swallowed():
         lightning_attn(q, q, q, torch.zeros(3, 1, 1, device=DEV))   # wrong head count
     with pytest.raises(TypeError):
         lightning_attn(q.double(), q.double(), q.double(), torch.zeros(2, 1, 1, device=DEV))
+
+
+# ---------------------------------------------------------------------------
+# tensor-core path (tcgen05 / TMEM / TMA): bf16, n a multiple of 128
+# ---------------------------------------------------------------------------
+TENSOR_SHAPES = [
+    (1, 1, 128, 128, 128),     # a single tile
+    (2, 3, 256, 128, 128),
+    (1, 2, 1024, 128, 128),
+    (2, 12, 2048, 128, 128),   # BASELINE config 1, one rank
+]
+
+
+@pytest.mark.parametrize("shape", TENSOR_SHAPES)
+@pytest.mark.parametrize("slopes", ["baseline", "steep", "zero"])
+def test_tensor_kernels_against_oracle(shape, slopes, monkeypatch):
+    from lasp_b200 import engine
+    b, h, n, d, e = shape
+    q, k, v, do = O.make_inputs(300 + n + h, b, h, n, d, e)
+    s = {"baseline": O.baseline_slopes(h), "steep": torch.full((h, 1, 1), 0.84),
+         "zero": torch.zeros(h, 1, 1)}[slopes]
+    assert engine.make_plan(b, h, n, d, e, torch.bfloat16, "auto").path_name == "tensor"
+    got = run_lightning(q, k, v, do, s, torch.bfloat16, "tensor", monkeypatch)
+    ref = oracle_on_rounded(q, k, v, do, s, torch.bfloat16)
+    for t, r, key in zip(got, ref, ("o", "dq", "dk", "dv")):
+        assert t.dtype == torch.bfloat16
+        assert O.max_rel_err(t, r) < TOL_BF16, (key, shape, slopes)
+    assert engine.read_status() == 0
+
+
+@pytest.mark.parametrize("sp", [2, 4])
+def test_tensor_rank_chain_equals_single_device(sp):
+    from lasp_b200 import engine
+    q, k, v, do = O.make_inputs(40 + sp, 2, 2, 256 * sp, 128, 128)
+    s = O.baseline_slopes(16)[[3, 12]]
+    got = _chain_on_one_gpu(q, k, v, do, s, sp, torch.bfloat16, "tensor")
+    ref = oracle_on_rounded(q, k, v, do, s, torch.bfloat16)
+    for t, r, key in zip(got, ref, ("o", "dq", "dk", "dv")):
+        assert O.max_rel_err(t, r) < TOL_BF16, (key, sp)
+    assert engine.read_status() == 0
+
+
+def test_tensor_path_outgoing_states_fp32():
+    from lasp_b200 import engine
+    b, h, n, d, e = 1, 2, 512, 128, 128
+    q, k, v, do = O.make_inputs(77, b, h, n, d, e)
+    s = O.baseline_slopes(2)
+    kv_in, dkv_in = torch.randn(b, h, d, e), torch.randn(b, h, d, e)
+    r = [t.to(torch.bfloat16).float() for t in (q, k, v, do)]
+    _, kv_ref = O.blocked_forward(r[0], r[1], r[2], s, kv_in)
+    *_, dkv_ref = O.blocked_backward(r[0], r[1], r[2], s, r[3], kv_in, dkv_in)
+    plan = engine.make_plan(b, h, n, d, e, torch.bfloat16, "tensor")
+    dev = [t.to(DEV, torch.bfloat16) for t in (q, k, v, do)]
+    kv_out, dkv_out = torch.empty(b, h, d, e, device=DEV), torch.empty(b, h, d, e, device=DEV)
+    fw = engine.Forward(plan, dev[0], dev[1], dev[2], s.to(DEV), kv_in=kv_in.to(DEV), kv_out=kv_out)
+    fw.run()
+    bw = engine.Backward(plan, dev[0], dev[1], dev[2], dev[3], s.to(DEV), fw.ws, dkv_in=dkv_in.to(DEV),
+                         dkv_out=dkv_out)
+    bw.run()
+    # states are accumulated in fp32 from bf16 products: far tighter than the bf16 output gate
+    assert O.max_rel_err(kv_out, kv_ref) < 2e-3
+    assert O.max_rel_err(dkv_out, dkv_ref) < 2e-3
