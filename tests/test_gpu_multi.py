@@ -1,0 +1,136 @@
+"""Sequence-parallel operators on real GPUs over NCCL (needs >= 2 devices).
+
+Every rank runs the four operators on its (dp_rank, sp_rank) chunk of seeded
+global tensors and checks O, dQ, dK, dV against the reference's golden outputs
+(tests/golden) or the CPU oracle's rank chain.
+"""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import lasp_oracle as O
+from tests.helpers import CASES, TOL_BF16, TOL_FP32, golden_tensor, load_golden, slopes_for, split
+
+pytestmark = pytest.mark.gpu
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run_variants(lasp, qi, ki, vi, doi, s):
+    bl, h, _, d = qi.shape
+    e = vi.shape[-1]
+    out = {}
+    for var in ("naive", "cache", "fuse", "fuse_parallel"):
+        qi.grad = ki.grad = vi.grad = None
+        qi.requires_grad_(True), ki.requires_grad_(True), vi.requires_grad_(True)
+        KV = torch.full((bl, h, d, e), float("nan"), device=qi.device)
+        DKV = torch.full((bl, h, d, e), float("nan"), device=qi.device)
+        if var == "naive":
+            oi = lasp.lasp_naive(qi, ki, vi, s)
+        elif var == "cache":
+            oi = lasp.lasp_cache(qi, ki, vi, s, torch.arange(qi.shape[2]).to(qi), KV, DKV)
+        else:
+            oi = getattr(lasp, "lasp_" + var)(qi, ki, vi, s, KV, DKV)
+        oi.backward(doi)
+        torch.cuda.synchronize()
+        out[var] = dict(o=oi.detach().float().cpu(), dq=qi.grad.float().cpu(), dk=ki.grad.float().cpu(),
+                        dv=vi.grad.float().cpu())
+        dist.barrier()
+    return out
+
+
+def _worker(rank, world, port, mode, params, errq):
+    try:
+        os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        import lasp
+        from lasp.utils import initialize_lasp
+        from lasp_b200 import engine
+        p = params
+        initialize_lasp(p["dp"], p["sp"])
+        dp_rank, sp_rank = rank // p["sp"], rank % p["sp"]
+        dtype = getattr(torch, p["dtype"])
+        q, k, v, do = O.make_inputs(p["seed"], p["b"], p["h"], p["n"], p["d"], p["e"])
+        s = slopes_for(p["slopes"], p["h"])
+        qi, ki, vi, doi = (split(t.to(dtype), p["dp"], p["sp"], dp_rank, sp_rank).to(dev) for t in (q, k, v, do))
+        got = _run_variants(lasp, qi, ki, vi, doi, s.to(dev))
+        if mode == "golden":
+            g = load_golden(p["name"])
+            tol = 1.5e-2 if dtype == torch.bfloat16 else TOL_FP32
+            for var, res in got.items():
+                ref_var = "naive" if var == "cache" else var
+                for nm, t in res.items():
+                    err = O.max_rel_err(t, golden_tensor(g[f"rank{rank}_{ref_var}_{nm}"]))
+                    assert err < tol, (var, nm, rank, err)
+        else:
+            # oracle rank chain on this rank's batch slice, a few heads only (heads are independent)
+            heads = p["check_heads"]
+            cast = (lambda t: t.to(dtype).float())
+            gq, gk, gv, gdo = (torch.cat([split(cast(t), p["dp"], p["sp"], dp_rank, r) for r in range(p["sp"])], 2)
+                               [:, heads] for t in (q, k, v, do))
+            outs, grads, _ = O.sp_chain(gq, gk, gv, s[heads], gdo, p["sp"])
+            ref = dict(o=outs[sp_rank], dq=grads[sp_rank][0], dk=grads[sp_rank][1], dv=grads[sp_rank][2])
+            tol = TOL_BF16 if dtype != torch.float32 else TOL_FP32
+            for var, res in got.items():
+                for nm, t in res.items():
+                    err = O.max_rel_err(t[:, heads], ref[nm])
+                    assert err < tol, (var, nm, rank, err)
+        assert engine.read_status() == 0
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as exc:  # noqa: BLE001
+        import traceback
+        errq.put(f"rank {rank}: {exc}\n{traceback.format_exc()}")
+        raise
+
+
+def _launch(world, mode, params):
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    try:
+        mp.spawn(_worker, args=(world, _free_port(), mode, params, errq), nprocs=world, join=True)
+    except Exception:
+        msgs = []
+        while not errq.empty():
+            msgs.append(errq.get())
+        pytest.fail("\n".join(msgs) or "worker failed")
+
+
+@pytest.mark.parametrize("name", ["sp2_fp32", "sp4_fp32", "dp2sp2_bf16"])
+def test_sequence_parallel_matches_reference_golden(name):
+    p = dict(CASES["sp"][name], name=name)
+    world = p["dp"] * p["sp"]
+    if _ngpu() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _launch(world, "golden", p)
+
+
+def _sweep():
+    n = _ngpu()
+    return [(dp, n // dp) for dp in (1, 2, 4, 8) if n >= 2 and n % dp == 0 and dp <= n]
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_dp_sp_sweep_baseline_config1(dtype):
+    """BASELINE config 1: every DP x SP factorisation of the box; per rank b=2,
+    2048 tokens, h=12, d=e=128 (bf16: tensor-core path; fp32: FFMA path)."""
+    if _ngpu() < 2:
+        pytest.skip("needs >= 2 GPUs")
+    for dp, sp in _sweep():
+        p = dict(seed=70 + dp, dp=dp, sp=sp, b=2 * dp, h=12, n=2048 * sp, d=128, e=128, slopes="baseline",
+                 dtype=dtype, check_heads=[0, 6, 11])
+        _launch(dp * sp, "oracle", p)
