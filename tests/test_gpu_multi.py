@@ -64,7 +64,12 @@ def _worker(rank, world, port, mode, params, errq):
         initialize_lasp(p["dp"], p["sp"])
         dp_rank, sp_rank = rank // p["sp"], rank % p["sp"]
         dtype = getattr(torch, p["dtype"])
-        q, k, v, do = O.make_inputs(p["seed"], p["b"], p["h"], p["n"], p["d"], p["e"])
+        if mode == "golden":
+            q, k, v, do = O.make_inputs(p["seed"], p["b"], p["h"], p["n"], p["d"], p["e"])
+        else:  # large global tensors: torch's generator is much faster and identical on every rank
+            g = torch.Generator().manual_seed(p["seed"])
+            q, k = (torch.randn(p["b"], p["h"], p["n"], p["d"], generator=g) * p["d"] ** -0.5 for _ in range(2))
+            v, do = (torch.randn(p["b"], p["h"], p["n"], p["e"], generator=g) for _ in range(2))
         s = slopes_for(p["slopes"], p["h"])
         qi, ki, vi, doi = (split(t.to(dtype), p["dp"], p["sp"], dp_rank, sp_rank).to(dev) for t in (q, k, v, do))
         got = _run_variants(lasp, qi, ki, vi, doi, s.to(dev))
