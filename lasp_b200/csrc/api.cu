@@ -60,8 +60,7 @@ int make_dims(const lasp_problem* p, lasp::Dims* m) {
 
 size_t workspace_bytes(const lasp::Dims& m) {
   size_t s = lasp::state_elems(m);
-  size_t bytes = s * 4;
-  if (m.path == LASP_PATH_TENSOR) bytes += s * 2;
+  size_t bytes = s * 4;  // fp32 states (SIMT) or bf16 local + bf16 prefix states (TENSOR)
   return (bytes + 255) & ~(size_t)255;
 }
 
@@ -141,7 +140,7 @@ int lasp_b200_fwd_chunk_states(const lasp_problem* p, const lasp_fwd_args* a, vo
   if (st != LASP_OK) return st;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (m.path == LASP_PATH_TENSOR)
-    return cuda_fail(lasp::tensor_chunk_states(m, a->k, a->v, a->s, lasp::ws_states_f32(a->ws), false, cs));
+    return cuda_fail(lasp::tensor_chunk_states(m, a->k, a->v, a->s, lasp::ws_local_bf16(a->ws), false, cs));
   return cuda_fail(lasp::simt_chunk_states(m, a->k, a->v, a->s, lasp::ws_states_f32(a->ws), false, cs));
 }
 
@@ -149,9 +148,11 @@ int lasp_b200_fwd_scan(const lasp_problem* p, const lasp_fwd_args* a, void* stre
   lasp::Dims m;
   int st = check_fwd(p, a, &m, false);
   if (st != LASP_OK) return st;
-  __nv_bfloat16* bf = (m.path == LASP_PATH_TENSOR) ? lasp::ws_states_bf16(a->ws, m) : nullptr;
-  return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_states_f32(a->ws), bf, a->kv_in, a->kv_out, false,
-                                     static_cast<cudaStream_t>(stream)));
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (m.path == LASP_PATH_TENSOR)
+    return cuda_fail(lasp::scan_states_bf16(m, a->s, lasp::ws_local_bf16(a->ws), lasp::ws_states_bf16(a->ws, m),
+                                            a->kv_in, a->kv_out, false, cs));
+  return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_states_f32(a->ws), a->kv_in, a->kv_out, false, cs));
 }
 
 int lasp_b200_fwd_output(const lasp_problem* p, const lasp_fwd_args* a, void* stream) {
@@ -180,7 +181,7 @@ int lasp_b200_bwd_chunk_states(const lasp_problem* p, const lasp_bwd_args* a, vo
   if (st != LASP_OK) return st;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (m.path == LASP_PATH_TENSOR)
-    return cuda_fail(lasp::tensor_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_states_f32(a->ws), true, cs));
+    return cuda_fail(lasp::tensor_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_local_bf16(a->ws), true, cs));
   return cuda_fail(lasp::simt_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_states_f32(a->ws), true, cs));
 }
 
@@ -188,9 +189,11 @@ int lasp_b200_bwd_scan(const lasp_problem* p, const lasp_bwd_args* a, void* stre
   lasp::Dims m;
   int st = check_bwd(p, a, &m, false);
   if (st != LASP_OK) return st;
-  __nv_bfloat16* bf = (m.path == LASP_PATH_TENSOR) ? lasp::ws_states_bf16(a->ws, m) : nullptr;
-  return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_states_f32(a->ws), bf, a->dkv_in, a->dkv_out, true,
-                                     static_cast<cudaStream_t>(stream)));
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (m.path == LASP_PATH_TENSOR)
+    return cuda_fail(lasp::scan_states_bf16(m, a->s, lasp::ws_local_bf16(a->ws), lasp::ws_states_bf16(a->ws, m),
+                                            a->dkv_in, a->dkv_out, true, cs));
+  return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_states_f32(a->ws), a->dkv_in, a->dkv_out, true, cs));
 }
 
 int lasp_b200_bwd_grads(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {

@@ -10,12 +10,13 @@
 namespace lasp {
 
 // Workspace layout (forward and backward use the same one):
-//   [0, S*4)                     fp32 chunk states, (b,h,nc,d,e); local states
-//                                after the chunk-state phase; on the SIMT path
-//                                the scan turns them into prefix states in place
-//   [.., .. + S*2)               TENSOR path only: bf16 prefix states written by
-//                                the scan, (b,h,nc,d,e) row-major (d rows, e cols)
-// with S = b*h*nc*d*e.
+//   SIMT path  : [0, S*4)   fp32 chunk states, (b,h,nc,d,e): local states after
+//                           the chunk-state phase; the scan turns them into
+//                           prefix states in place
+//   TENSOR path: [0, S*2)   bf16 local chunk states, (b,h,nc,d,e)
+//                [S*2, S*4) bf16 prefix states written by the scan (the MMA
+//                           operand), (b,h,nc,d,e) row-major (d rows, e cols)
+// with S = b*h*nc*d*e.  The running prefix inside the scan is always fp32.
 constexpr int kSimtChunk = 64;     // the reference's block size
 constexpr int kTensorChunk = 128;  // one tcgen05 M=128 tile
 
@@ -33,11 +34,13 @@ inline float* ws_states_f32(void* ws) { return reinterpret_cast<float*>(static_c
 inline const float* ws_states_f32(const void* ws) {
   return reinterpret_cast<const float*>(static_cast<const char*>(ws));
 }
+// tensor path: bf16 local states at offset 0, bf16 prefix states after them
+inline __nv_bfloat16* ws_local_bf16(void* ws) { return reinterpret_cast<__nv_bfloat16*>(ws); }
 inline __nv_bfloat16* ws_states_bf16(void* ws, const Dims& m) {
-  return reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + state_elems(m) * 4);
+  return reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + state_elems(m) * 2);
 }
 inline const __nv_bfloat16* ws_states_bf16(const void* ws, const Dims& m) {
-  return reinterpret_cast<const __nv_bfloat16*>(static_cast<const char*>(ws) + state_elems(m) * 4);
+  return reinterpret_cast<const __nv_bfloat16*>(static_cast<const char*>(ws) + state_elems(m) * 2);
 }
 
 // bits of the sticky per-device fault word (tensor_kernels.cu owns the word)
@@ -54,8 +57,10 @@ extern thread_local const char* g_failed_step;
 // ---- launchers implemented in the .cu files (return cudaError_t) -----------
 cudaError_t simt_chunk_states(const Dims& m, const void* a, const void* bten, const float* s, float* states,
                               bool backward, cudaStream_t st);
-cudaError_t scan_states(const Dims& m, const float* s, float* states, __nv_bfloat16* states_bf16,
-                        const float* x_in, float* x_out, bool reverse, cudaStream_t st);
+cudaError_t scan_states(const Dims& m, const float* s, float* states, const float* x_in, float* x_out, bool reverse,
+                        cudaStream_t st);
+cudaError_t scan_states_bf16(const Dims& m, const float* s, const __nv_bfloat16* local, __nv_bfloat16* prefix,
+                             const float* x_in, float* x_out, bool reverse, cudaStream_t st);
 cudaError_t simt_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
                             const float* prefix, void* o, cudaStream_t st);
 cudaError_t simt_bwd_grads(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
@@ -65,8 +70,8 @@ cudaError_t state_combine(int b, int h, int d, int e, int n, const float* s, con
                           const float* x_local, float* x_out, cudaStream_t st);
 
 // tcgen05 path (tensor_kernels.cu)
-cudaError_t tensor_chunk_states(const Dims& m, const void* a, const void* bten, const float* s, float* states,
-                                bool backward, cudaStream_t st);
+cudaError_t tensor_chunk_states(const Dims& m, const void* a, const void* bten, const float* s,
+                                __nv_bfloat16* states, bool backward, cudaStream_t st);
 cudaError_t tensor_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
                               const __nv_bfloat16* prefix, void* o, cudaStream_t st);
 cudaError_t tensor_bwd_grads(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,

@@ -87,14 +87,62 @@ __global__ void __launch_bounds__(NT) k_chunk_states(const T* __restrict__ A, co
 
 // ---------------------------------------------------------------------------
 // scan over chunks, elementwise in (d,e).  forward: exclusive prefix seeded
-// with x_in; reverse: exclusive suffix.  Writes the prefix states in place
-// (fp32) or, when out_bf16 != nullptr, as bf16 into that buffer instead (the
-// tensor-core operand copy; the fp32 local states are then left untouched).
+// with x_in; reverse: exclusive suffix.  k_scan turns fp32 local states into
+// prefix states in place; k_scan_bf16 reads bf16 local states and writes bf16
+// prefix states into a second buffer (the tensor-core operand).  The running
+// value is fp32 in both.  Loads of a batch of chunks are issued before the
+// dependent recurrence so that their latencies overlap.
 // ---------------------------------------------------------------------------
+constexpr int kScanBatch = 8;
+
+__global__ void __launch_bounds__(256) k_scan_bf16(const float* __restrict__ s,
+                                                   const __nv_bfloat16* __restrict__ local,
+                                                   __nv_bfloat16* __restrict__ prefix,
+                                                   const float* __restrict__ x_in, float* __restrict__ x_out, int h,
+                                                   int n, int de, int nc, int chunk, int reverse) {
+  const int bh = blockIdx.y;
+  const int el = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (el >= de) return;
+  const float sh = s[bh % h];
+  const float full = expf(-sh * (float)chunk);
+  const float tail = expf(-sh * (float)(n - (nc - 1) * chunk));
+  float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (x_in) p = *reinterpret_cast<const float4*>(x_in + (size_t)bh * de + el);
+  const __nv_bfloat16* lbase = local + (size_t)bh * nc * de + el;
+  __nv_bfloat16* pbase = prefix + (size_t)bh * nc * de + el;
+  for (int i0 = 0; i0 < nc; i0 += kScanBatch) {
+    uint2 loc[kScanBatch];
+#pragma unroll
+    for (int u = 0; u < kScanBatch; ++u) {
+      const int i = i0 + u;
+      if (i < nc) loc[u] = *reinterpret_cast<const uint2*>(lbase + (size_t)(reverse ? nc - 1 - i : i) * de);
+    }
+#pragma unroll
+    for (int u = 0; u < kScanBatch; ++u) {
+      const int i = i0 + u;
+      if (i < nc) {
+        const int c = reverse ? nc - 1 - i : i;
+        __nv_bfloat162 lo = __floats2bfloat162_rn(p.x, p.y), hi = __floats2bfloat162_rn(p.z, p.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(pbase + (size_t)c * de) = pk;
+        const float dec = (c == nc - 1) ? tail : full;
+        const float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&loc[u].x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&loc[u].y));
+        p.x = fmaf(dec, p.x, a.x);
+        p.y = fmaf(dec, p.y, a.y);
+        p.z = fmaf(dec, p.z, b.x);
+        p.w = fmaf(dec, p.w, b.y);
+      }
+    }
+  }
+  if (x_out) *reinterpret_cast<float4*>(x_out + (size_t)bh * de + el) = p;
+}
+
 __global__ void __launch_bounds__(256) k_scan(const float* __restrict__ s, float* __restrict__ states,
-                                              __nv_bfloat16* __restrict__ out_bf16, const float* __restrict__ x_in,
-                                              float* __restrict__ x_out, int h, int n, int de, int nc, int chunk,
-                                              int reverse) {
+                                              const float* __restrict__ x_in, float* __restrict__ x_out, int h,
+                                              int n, int de, int nc, int chunk, int reverse) {
   const int bh = blockIdx.y;
   const int el = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (el >= de) return;
@@ -105,24 +153,26 @@ __global__ void __launch_bounds__(256) k_scan(const float* __restrict__ s, float
   float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
   if (x_in) p = *reinterpret_cast<const float4*>(x_in + (size_t)bh * de + el);
   float* base = states + (size_t)bh * nc * de + el;
-  __nv_bfloat16* bbase = out_bf16 ? out_bf16 + (size_t)bh * nc * de + el : nullptr;
-  for (int i = 0; i < nc; ++i) {
-    const int c = reverse ? nc - 1 - i : i;
-    const float dec = (c == nc - 1) ? tail : full;
-    float4 loc = *reinterpret_cast<const float4*>(base + (size_t)c * de);
-    if (!bbase) {
-      *reinterpret_cast<float4*>(base + (size_t)c * de) = p;
-    } else {
-      __nv_bfloat162 lo = __floats2bfloat162_rn(p.x, p.y), hi = __floats2bfloat162_rn(p.z, p.w);
-      uint2 pk;
-      pk.x = *reinterpret_cast<uint32_t*>(&lo);
-      pk.y = *reinterpret_cast<uint32_t*>(&hi);
-      *reinterpret_cast<uint2*>(bbase + (size_t)c * de) = pk;
+  for (int i0 = 0; i0 < nc; i0 += kScanBatch) {
+    float4 loc[kScanBatch];
+#pragma unroll
+    for (int u = 0; u < kScanBatch; ++u) {
+      const int i = i0 + u;
+      if (i < nc) loc[u] = *reinterpret_cast<const float4*>(base + (size_t)(reverse ? nc - 1 - i : i) * de);
     }
-    p.x = fmaf(dec, p.x, loc.x);
-    p.y = fmaf(dec, p.y, loc.y);
-    p.z = fmaf(dec, p.z, loc.z);
-    p.w = fmaf(dec, p.w, loc.w);
+#pragma unroll
+    for (int u = 0; u < kScanBatch; ++u) {
+      const int i = i0 + u;
+      if (i < nc) {
+        const int c = reverse ? nc - 1 - i : i;
+        const float dec = (c == nc - 1) ? tail : full;
+        *reinterpret_cast<float4*>(base + (size_t)c * de) = p;
+        p.x = fmaf(dec, p.x, loc[u].x);
+        p.y = fmaf(dec, p.y, loc[u].y);
+        p.z = fmaf(dec, p.z, loc[u].z);
+        p.w = fmaf(dec, p.w, loc[u].w);
+      }
+    }
   }
   if (x_out) *reinterpret_cast<float4*>(x_out + (size_t)bh * de + el) = p;
 }
@@ -419,11 +469,19 @@ cudaError_t simt_chunk_states(const Dims& m, const void* a, const void* bten, co
   return cudaGetLastError();
 }
 
-cudaError_t scan_states(const Dims& m, const float* s, float* states, __nv_bfloat16* states_bf16,
-                        const float* x_in, float* x_out, bool reverse, cudaStream_t st) {
+cudaError_t scan_states(const Dims& m, const float* s, float* states, const float* x_in, float* x_out, bool reverse,
+                        cudaStream_t st) {
   const int de = m.d * m.e;
   dim3 grid((de / 4 + 255) / 256, m.b * m.h);
-  k_scan<<<grid, 256, 0, st>>>(s, states, states_bf16, x_in, x_out, m.h, m.n, de, m.nc, m.chunk, reverse ? 1 : 0);
+  k_scan<<<grid, 256, 0, st>>>(s, states, x_in, x_out, m.h, m.n, de, m.nc, m.chunk, reverse ? 1 : 0);
+  return cudaGetLastError();
+}
+
+cudaError_t scan_states_bf16(const Dims& m, const float* s, const __nv_bfloat16* local, __nv_bfloat16* prefix,
+                             const float* x_in, float* x_out, bool reverse, cudaStream_t st) {
+  const int de = m.d * m.e;
+  dim3 grid((de / 4 + 127) / 128, m.b * m.h);
+  k_scan_bf16<<<grid, 128, 0, st>>>(s, local, prefix, x_in, x_out, m.h, m.n, de, m.nc, m.chunk, reverse ? 1 : 0);
   return cudaGetLastError();
 }
 

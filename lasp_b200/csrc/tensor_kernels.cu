@@ -10,6 +10,7 @@
 // All waits are bounded; a wait that runs out sets a bit in g_fault_word and the
 // CTA skips its remaining waits, frees its tensor memory and exits.
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "sm100.cuh"
@@ -53,31 +54,6 @@ __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
   return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
 }
 
-// tab[i] = exp(-s i), i = 0..C
-__device__ __forceinline__ void fill_decay_table(float* tab, float s) {
-  for (int i = threadIdx.x; i <= C; i += blockDim.x) tab[i] = expf(-s * (float)i);
-}
-
-// Tensor-memory accumulator (32 columns at `taddr` for this thread's lane) ->
-// decay-masked bf16 in a K-major swizzled tile: out[row][col0+j] = [row >= col] tab[row-col] acc.
-__device__ __forceinline__ void masked_store32(uint32_t taddr, uint8_t* tile, int row, int col0, const float* tab) {
-  uint32_t r[32];
-  tmem_ld32(taddr, r);
-  tmem_ld_wait();
-#pragma unroll
-  for (int j = 0; j < 32; j += 8) {
-    uint32_t pk[4];
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const int c0 = col0 + j + 2 * t, c1 = c0 + 1;
-      const float a = (row >= c0) ? __uint_as_float(r[j + 2 * t]) * tab[row - c0] : 0.f;
-      const float b = (row >= c1) ? __uint_as_float(r[j + 2 * t + 1]) * tab[row - c1] : 0.f;
-      pk[t] = pack_bf16(a, b);
-    }
-    *reinterpret_cast<uint4*>(tile + tile_offset(row, col0 + j, C)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-  }
-}
-
 // acc (32 columns) *= f, in tensor memory
 __device__ __forceinline__ void scale_tmem32(uint32_t taddr, float f) {
   uint32_t r[32];
@@ -112,14 +88,40 @@ __device__ __forceinline__ void store_row32(uint32_t taddr1, uint32_t taddr2, fl
   }
 }
 
+// tile[row][col0 .. col0+31] = bf16(acc1 + f * acc2) into a swizzled staging tile of C rows
+// (acc2 skipped when taddr2 == 0xFFFFFFFF); a TMA store then moves the tile out
+__device__ __forceinline__ void stage_row32(uint32_t taddr1, uint32_t taddr2, float f, uint8_t* tile, int row,
+                                            int col0) {
+  uint32_t a[32];
+  tmem_ld32(taddr1, a);
+  if (taddr2 != 0xFFFFFFFFu) {
+    uint32_t b[32];
+    tmem_ld32(taddr2, b);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) a[j] = __float_as_uint(fmaf(f, __uint_as_float(b[j]), __uint_as_float(a[j])));
+  } else {
+    tmem_ld_wait();
+  }
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    uint4 v = make_uint4(pack_bf16(__uint_as_float(a[j]), __uint_as_float(a[j + 1])),
+                         pack_bf16(__uint_as_float(a[j + 2]), __uint_as_float(a[j + 3])),
+                         pack_bf16(__uint_as_float(a[j + 4]), __uint_as_float(a[j + 5])),
+                         pack_bf16(__uint_as_float(a[j + 6]), __uint_as_float(a[j + 7])));
+    *reinterpret_cast<uint4*>(tile + tile_offset(row, col0 + j, C)) = v;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // chunk states: out[i][j] = sum_c w_c A[c][i] B[c][j]   (A = K or Q, B = V or dO)
 // ---------------------------------------------------------------------------
 template <int D, int E>
 __global__ void __launch_bounds__(128) k_tc_chunk_states(const __grid_constant__ CUtensorMap map_a,
                                                          const __grid_constant__ CUtensorMap map_b,
-                                                         const float* __restrict__ s, float* __restrict__ states,
-                                                         int h, int n, int nc, int backward) {
+                                                         const float* __restrict__ s,
+                                                         __nv_bfloat16* __restrict__ states, int h, int n, int nc,
+                                                         int backward) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   uint8_t* sa = smem;               // C x D  (followed by sb: with D = 64 the M = 128 MMA reads on into sb)
@@ -183,17 +185,10 @@ __global__ void __launch_bounds__(128) k_tc_chunk_states(const __grid_constant__
   wait_or_fault(&bar_mma, 0, &dead, kFaultMmaWait);
   tc_fence_after_sync();
   if (tid < D) {
-    float* out = states + ((size_t)bh * nc + chunk) * D * E + (size_t)tid * E;
+    __nv_bfloat16* out = states + ((size_t)bh * nc + chunk) * D * E + (size_t)tid * E;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
 #pragma unroll
-    for (int c0 = 0; c0 < E; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(tmem + lane_base + c0, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        *reinterpret_cast<uint4*>(out + c0 + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-    }
+    for (int c0 = 0; c0 < E; c0 += 32) store_row32(tmem + lane_base + c0, 0xFFFFFFFFu, 0.f, out, c0);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -201,112 +196,199 @@ __global__ void __launch_bounds__(128) k_tc_chunk_states(const __grid_constant__
 }
 
 // ---------------------------------------------------------------------------
-// forward output: O = S_m V + diag(lambda^r) Q P
+// forward output: O = S_m V + diag(lambda^r) Q P      (persistent, pipelined)
+//
+// One CTA per SM walks over tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...
+// Ten warps in three roles, synchronised only through mbarriers:
+//   warp 0 (one lane)  producer: TMA loads of Q, P (single buffers) and K, V
+//                      (two buffers each), issued as soon as a buffer is free
+//   warp 1 (one lane)  tensor-core issuer: S = Q K^T and O2 = Q P, then, once
+//                      S_m is in shared memory, O1 = S_m V over S's columns
+//   warps 2-9          S -> decay mask -> S_m (bf16, over the K buffer);
+//                      epilogue O = O1 + lambda^r O2 -> global
+// Tensor memory is double buffered (256 columns per tile parity), so the loads
+// and the first MMAs of tile i+1 overlap the mask and epilogue work of tile i.
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ float decay_pow(float sl2, int k) { return exp2f(-sl2 * (float)k); }
+
+// Tensor-memory accumulator (32 columns at `taddr`, this thread's lane = row) ->
+// decay-masked bf16 in a K-major swizzled tile:
+//   out[row][col] = [row >= col] lambda^(row-col) acc[col].
+// The factor is built from the right-most unmasked column leftwards by repeated
+// multiplication with lambda, so it can only underflow towards the far columns.
+__device__ __forceinline__ void masked_store32(uint32_t taddr, uint8_t* tile, int row, int col0, float sl2,
+                                               float lam) {
+  uint32_t r[32];
+  tmem_ld32(taddr, r);
+  tmem_ld_wait();
+  const int first = min(row, col0 + 31);  // right-most column of this group with row >= col
+  float f = decay_pow(sl2, row - first);
+  float m[32];
+#pragma unroll
+  for (int j = 31; j >= 0; --j) {
+    const bool live = (col0 + j) <= row;
+    m[j] = live ? __uint_as_float(r[j]) * f : 0.f;
+    f = live ? f * lam : f;
+  }
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    const uint4 v = make_uint4(pack_bf16(m[j], m[j + 1]), pack_bf16(m[j + 2], m[j + 3]), pack_bf16(m[j + 4], m[j + 5]),
+                               pack_bf16(m[j + 6], m[j + 7]));
+    *reinterpret_cast<uint4*>(tile + tile_offset(row, col0 + j, C)) = v;
+  }
+}
+
+constexpr float kLog2e = 1.4426950408889634f;
+
 template <int D, int E>
-__global__ void __launch_bounds__(256) k_tc_fwd_output(const __grid_constant__ CUtensorMap map_q,
-                                                       const __grid_constant__ CUtensorMap map_k,
-                                                       const __grid_constant__ CUtensorMap map_v,
-                                                       const __grid_constant__ CUtensorMap map_p,
-                                                       const float* __restrict__ s, __nv_bfloat16* __restrict__ O,
-                                                       int h, int n, int nc) {
+__global__ void __launch_bounds__(320, 1) k_tc_fwd_output(const __grid_constant__ CUtensorMap map_q,
+                                                          const __grid_constant__ CUtensorMap map_k,
+                                                          const __grid_constant__ CUtensorMap map_v,
+                                                          const __grid_constant__ CUtensorMap map_p,
+                                                          const __grid_constant__ CUtensorMap map_o,
+                                                          const float* __restrict__ s, int h, int n, int nc,
+                                                          int num_tiles) {
+  constexpr int kQ = C * D * 2, kP = D * E * 2, kK = C * C * 2 /* K, then S_m; C >= D */, kV = C * E * 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
-  uint8_t* sq = smem;                  // C x D
-  uint8_t* sv = sq + C * D * 2;        // C x E
-  uint8_t* sp = sv + C * E * 2;        // D x E
-  uint8_t* sk = sp + D * E * 2;        // C x D, then S_m (C x C) - kept last and sized for the larger
-  __shared__ uint64_t bar_qk, bar_vp, bar_s, bar_o;
+  uint8_t* sq = smem;
+  uint8_t* sp = sq + kQ;
+  uint8_t* sk[2] = {sp + kP, sp + kP + kK};
+  uint8_t* sv[2] = {sp + kP + 2 * kK, sp + kP + 2 * kK + kV};
+  uint8_t* so = sv[1] + kV;  // C x E staging tile of the output
+  __shared__ uint64_t qp_full, k_full[2], v_full[2], s_full[2], sm_ready[2], o_full[2], t_free[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int dead;
-  __shared__ float tab[C + 1];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int chunk = blockIdx.x, bh = blockIdx.y;
-  const float sh = s[bh % h];
   if (tid == 0) {
     dead = 0;
-    mbar_init(&bar_qk, 1);
-    mbar_init(&bar_vp, 1);
-    mbar_init(&bar_s, 1);
-    mbar_init(&bar_o, 1);
+    mbar_init(&qp_full, 1);
+    for (int p = 0; p < 2; ++p) {
+      mbar_init(&k_full[p], 1);
+      mbar_init(&v_full[p], 1);
+      mbar_init(&s_full[p], 1);
+      mbar_init(&sm_ready[p], 256);
+      mbar_init(&o_full[p], 1);
+      mbar_init(&t_free[p], 256);
+    }
     fence_mbar_init();
   }
-  if (warp == 0) tmem_alloc(&tmem_slot, 512);
-  fill_decay_table(tab, sh);
+  if (warp == 2) tmem_alloc(&tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
-  const uint32_t t_s = tmem, t_o2 = tmem + 128, t_o1 = tmem + 256;
-  const int row0 = bh * n + chunk * C;
-  if (tid == 0) {
-    mbar_expect_tx(&bar_qk, 2 * C * D * 2);
-    tma_load_3d(sq, &map_q, &bar_qk, 0, row0, 0);
-    tma_load_3d(sk, &map_k, &bar_qk, 0, row0, 0);
-    mbar_expect_tx(&bar_vp, (C * E + D * E) * 2);
-    tma_load_3d(sv, &map_v, &bar_vp, 0, row0, 0);
-    tma_load_3d(sp, &map_p, &bar_vp, 0, (bh * nc + chunk) * D, 0);
-    wait_or_fault(&bar_qk, 0, &dead, kFaultTmaWait);
-    if (!dead) {
-      tc_fence_after_sync();
-      umma_gemm(t_s, Operand{smem_u32(sq), C, false}, Operand{smem_u32(sk), C, false}, C, D / 16, false);
-      umma_commit(&bar_s);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int i = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++i) {
+        const int bh = t / nc, chunk = t - bh * nc, row0 = bh * n + chunk * C, p = i & 1;
+        if (i >= 2) wait_or_fault(&o_full[p], ((i - 2) >> 1) & 1, &dead, kFaultMmaWait);  // K/S_m, V of tile i-2 read
+        mbar_expect_tx(&k_full[p], kQ);
+        tma_load_3d(sk[p], &map_k, &k_full[p], 0, row0, 0);
+        mbar_expect_tx(&v_full[p], kV);
+        tma_load_3d(sv[p], &map_v, &v_full[p], 0, row0, 0);
+        if (i >= 1) wait_or_fault(&s_full[(i - 1) & 1], ((i - 1) >> 1) & 1, &dead, kFaultMmaWait);  // Q, P read
+        mbar_expect_tx(&qp_full, kQ + kP);
+        tma_load_3d(sq, &map_q, &qp_full, 0, row0, 0);
+        tma_load_3d(sp, &map_p, &qp_full, 0, (bh * nc + chunk) * D, 0);
+      }
     }
-    wait_or_fault(&bar_vp, 0, &dead, kFaultTmaWait);
-    if (!dead) {
-      tc_fence_after_sync();
-      umma_gemm(t_o2, Operand{smem_u32(sq), C, false}, Operand{smem_u32(sp), D, true}, E, D / 16, false);
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int i = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++i) {
+        const int p = i & 1, ph2 = (i >> 1) & 1;
+        const uint32_t t_s = tmem + 256 * p, t_o2 = t_s + 128;
+        if (i >= 2) wait_or_fault(&t_free[p], ((i - 2) >> 1) & 1, &dead, kFaultMmaWait);
+        wait_or_fault(&qp_full, i & 1, &dead, kFaultTmaWait);
+        wait_or_fault(&k_full[p], ph2, &dead, kFaultTmaWait);
+        tc_fence_after_sync();
+        umma_gemm(t_s, Operand{smem_u32(sq), C, false}, Operand{smem_u32(sk[p]), C, false}, C, D / 16, false);
+        umma_gemm(t_o2, Operand{smem_u32(sq), C, false}, Operand{smem_u32(sp), D, true}, E, D / 16, false);
+        umma_commit(&s_full[p]);
+        wait_or_fault(&sm_ready[p], ph2, &dead, kFaultMmaWait);
+        wait_or_fault(&v_full[p], ph2, &dead, kFaultTmaWait);
+        tc_fence_after_sync();
+        umma_gemm(t_s, Operand{smem_u32(sk[p]), C, false}, Operand{smem_u32(sv[p]), C, true}, E, C / 16, false);
+        umma_commit(&o_full[p]);
+      }
     }
-  }
-  __syncwarp();
-  wait_or_fault(&bar_s, 0, &dead, kFaultMmaWait);
-  tc_fence_after_sync();
-  const int row = (warp & 3) * 32 + lane;
-  const int half = warp >> 2;
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  // S -> S_m (bf16) over the K tile
+  } else {
+    const int cw = warp - 2;                       // 0..7
+    const int row = (warp & 3) * 32 + lane;        // tensor-memory lane quarter of this warp
+    const int half = cw >> 2;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    int i = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++i) {
+      const int bh = t / nc, chunk = t - bh * nc, row0 = bh * n + chunk * C, p = i & 1, ph2 = (i >> 1) & 1;
+      const uint32_t t_s = tmem + 256 * p, t_o2 = t_s + 128;
+      const float sl2 = s[bh % h] * kLog2e;
+      const float lam = exp2f(-sl2);
+      wait_or_fault(&s_full[p], ph2, &dead, kFaultMmaWait);
+      tc_fence_after_sync();
 #pragma unroll
-  for (int cc = 0; cc < 2; ++cc) {
-    const int col0 = half * 64 + cc * 32;
-    masked_store32(t_s + lane_base + col0, sk, row, col0, tab);
+      for (int cc = 0; cc < 2; ++cc) {
+        const int col0 = half * 64 + cc * 32;
+        masked_store32(t_s + lane_base + col0, sk[p], row, col0, sl2, lam);
+      }
+      fence_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&sm_ready[p]);
+      wait_or_fault(&o_full[p], ph2, &dead, kFaultMmaWait);
+      tc_fence_after_sync();
+      // the staging tile is free once the previous tile's store has read it
+      if (cw == 0 && lane == 0) bulk_wait_read<0>();
+      named_sync(1, 256);
+      const float qd = decay_pow(sl2, row);
+#pragma unroll
+      for (int cc = 0; cc < E / 64; ++cc) {
+        const int col0 = half * (E / 2) + cc * 32;
+        stage_row32(t_s + lane_base + col0, t_o2 + lane_base + col0, qd, so, row, col0);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&t_free[p]);
+      fence_async_smem();
+      named_sync(1, 256);
+      if (cw == 0 && lane == 0) {
+        tma_store_3d(&map_o, so, 0, row0, 0);
+        bulk_commit();
+      }
+    }
+    if (cw == 0 && lane == 0) bulk_wait_all<0>();
   }
-  fence_async_smem();
   tc_fence_before_sync();
   __syncthreads();
-  if (tid == 0 && !dead) {
-    tc_fence_after_sync();
-    umma_gemm(t_o1, Operand{smem_u32(sk), C, false}, Operand{smem_u32(sv), C, true}, E, C / 16, false);
-    umma_commit(&bar_o);
-  }
-  __syncwarp();
-  wait_or_fault(&bar_o, 0, &dead, kFaultMmaWait);
-  tc_fence_after_sync();
-  {
-    __nv_bfloat16* out_row = O + (size_t)(row0 + row) * E;
-    const float qd = tab[row];
-#pragma unroll
-    for (int cc = 0; cc < E / 64; ++cc) {
-      const int col0 = half * (E / 2) + cc * 32;
-      store_row32(t_o1 + lane_base + col0, t_o2 + lane_base + col0, qd, out_row, col0);
-    }
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
+  if (warp == 2) tmem_dealloc(tmem, 512);
 }
 
 // ---------------------------------------------------------------------------
 // backward: dQ = dS_m K + diag(lambda^r) dO P^T
 //           dK = dS_m^T Q + diag(lambda^(C-c)) V Dn^T
-//           dV = S_m^T dO + diag(lambda^(C-c)) K Dn
+//           dV = S_m^T dO + diag(lambda^(C-c)) K Dn          (persistent)
+//
+// Seven shared-memory tiles (Q, K, V, dO, Dn, dS_m, P -> S_m) and all 512
+// tensor-memory columns are in use, so tiles cannot be double buffered; what
+// overlaps is the next tile's six loads with this tile's epilogue.
+//   warp 0 (one lane)  producer: as soon as the last MMAs of tile i have
+//                      completed, loads tile i+1 into the same buffers
+//   warp 1 (one lane)  tensor-core issuer.  Phase A: S = Q K^T (T0),
+//                      dS = dO V^T (T1), dO P^T (T2), V Dn^T (T3).  Phase B,
+//                      after the warps below: T2 += dS_m K, T3 += dS_m^T Q,
+//                      T0 = S_m^T dO, T1 = K Dn
+//   warps 2-9          S, dS -> decay mask -> S_m, dS_m in shared memory; T2, T3
+//                      scaled by their row decays in place; epilogue dQ = T2,
+//                      dK = T3, dV = T0 + lambda^(C-c) T1, staged one after the
+//                      other through the dS_m tile and stored by TMA
 // ---------------------------------------------------------------------------
 template <int D, int E>
-__global__ void __launch_bounds__(256) k_tc_bwd_grads(
+__global__ void __launch_bounds__(320, 1) k_tc_bwd_grads(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
     const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_dn,
-    const float* __restrict__ s, __nv_bfloat16* __restrict__ DQ, __nv_bfloat16* __restrict__ DK,
-    __nv_bfloat16* __restrict__ DV, int h, int n, int nc) {
+    const __grid_constant__ CUtensorMap map_dq, const __grid_constant__ CUtensorMap map_dk,
+    const __grid_constant__ CUtensorMap map_dv, const float* __restrict__ s, int h, int n, int nc, int num_tiles) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   uint8_t* sq = smem;                   // C x D
@@ -314,113 +396,150 @@ __global__ void __launch_bounds__(256) k_tc_bwd_grads(
   uint8_t* sv = sk + C * D * 2;         // C x E
   uint8_t* sdo = sv + C * E * 2;        // C x E
   uint8_t* sdn = sdo + C * E * 2;       // D x E  suffix state
-  uint8_t* sds = sdn + D * E * 2;       // C x C  dS_m
+  uint8_t* sds = sdn + D * E * 2;       // C x C  dS_m, then the staging tile of the epilogue
   uint8_t* sp = sds + C * C * 2;        // D x E  prefix state, then S_m (C x C)
-  __shared__ uint64_t bar_in, bar_st, bar_a, bar_b;
+  __shared__ uint64_t bar_in, bar_st, a_done, sm_ready, b_done, t_free;
   __shared__ uint32_t tmem_slot;
   __shared__ int dead;
-  __shared__ float tab[C + 1];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int chunk = blockIdx.x, bh = blockIdx.y;
-  const float sh = s[bh % h];
   if (tid == 0) {
     dead = 0;
     mbar_init(&bar_in, 1);
     mbar_init(&bar_st, 1);
-    mbar_init(&bar_a, 1);
-    mbar_init(&bar_b, 1);
+    mbar_init(&a_done, 1);
+    mbar_init(&sm_ready, 256);
+    mbar_init(&b_done, 1);
+    mbar_init(&t_free, 256);
     fence_mbar_init();
   }
-  if (warp == 0) tmem_alloc(&tmem_slot, 512);
-  fill_decay_table(tab, sh);
+  if (warp == 2) tmem_alloc(&tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
   const uint32_t t0 = tmem, t1 = tmem + 128, t2 = tmem + 256, t3 = tmem + 384;
-  const int row0 = bh * n + chunk * C;
-  if (tid == 0) {
-    mbar_expect_tx(&bar_in, 2 * C * (D + E) * 2);
-    tma_load_3d(sq, &map_q, &bar_in, 0, row0, 0);
-    tma_load_3d(sk, &map_k, &bar_in, 0, row0, 0);
-    tma_load_3d(sv, &map_v, &bar_in, 0, row0, 0);
-    tma_load_3d(sdo, &map_do, &bar_in, 0, row0, 0);
-    mbar_expect_tx(&bar_st, 2 * D * E * 2);
-    tma_load_3d(sp, &map_p, &bar_st, 0, (bh * nc + chunk) * D, 0);
-    tma_load_3d(sdn, &map_dn, &bar_st, 0, (bh * nc + chunk) * D, 0);
-    wait_or_fault(&bar_in, 0, &dead, kFaultTmaWait);
-    if (!dead) {
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int i = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++i) {
+        const int bh = t / nc, chunk = t - bh * nc, row0 = bh * n + chunk * C;
+        if (i >= 1) wait_or_fault(&b_done, (i - 1) & 1, &dead, kFaultMmaWait);  // every buffer of tile i-1 is read
+        mbar_expect_tx(&bar_in, 2 * C * (D + E) * 2);
+        tma_load_3d(sq, &map_q, &bar_in, 0, row0, 0);
+        tma_load_3d(sk, &map_k, &bar_in, 0, row0, 0);
+        tma_load_3d(sdo, &map_do, &bar_in, 0, row0, 0);
+        tma_load_3d(sv, &map_v, &bar_in, 0, row0, 0);
+        mbar_expect_tx(&bar_st, 2 * D * E * 2);
+        tma_load_3d(sp, &map_p, &bar_st, 0, (bh * nc + chunk) * D, 0);
+        tma_load_3d(sdn, &map_dn, &bar_st, 0, (bh * nc + chunk) * D, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int i = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++i) {
+        const uint32_t ph = i & 1;
+        if (i >= 1) wait_or_fault(&t_free, (i - 1) & 1, &dead, kFaultMmaWait);  // epilogue of tile i-1 has drained T0..T3
+        wait_or_fault(&bar_in, ph, &dead, kFaultTmaWait);
+        tc_fence_after_sync();
+        umma_gemm(t0, Operand{smem_u32(sq), C, false}, Operand{smem_u32(sk), C, false}, C, D / 16, false);
+        umma_gemm(t1, Operand{smem_u32(sdo), C, false}, Operand{smem_u32(sv), C, false}, C, E / 16, false);
+        wait_or_fault(&bar_st, ph, &dead, kFaultTmaWait);
+        tc_fence_after_sync();
+        // state tiles as K-major B operands: rows = d (N), columns = e (K)
+        umma_gemm(t2, Operand{smem_u32(sdo), C, false}, Operand{smem_u32(sp), D, false}, D, E / 16, false);
+        umma_gemm(t3, Operand{smem_u32(sv), C, false}, Operand{smem_u32(sdn), D, false}, D, E / 16, false);
+        umma_commit(&a_done);
+        wait_or_fault(&sm_ready, ph, &dead, kFaultMmaWait);
+        tc_fence_after_sync();
+        umma_gemm(t2, Operand{smem_u32(sds), C, false}, Operand{smem_u32(sk), C, true}, D, C / 16, true);
+        umma_gemm(t3, Operand{smem_u32(sds), C, true}, Operand{smem_u32(sq), C, true}, D, C / 16, true);
+        umma_gemm(t0, Operand{smem_u32(sp), C, true}, Operand{smem_u32(sdo), C, true}, E, C / 16, false);
+        umma_gemm(t1, Operand{smem_u32(sk), C, false}, Operand{smem_u32(sdn), D, true}, E, D / 16, false);
+        umma_commit(&b_done);
+      }
+    }
+  } else {
+    const int cw = warp - 2;
+    const int row = (warp & 3) * 32 + lane;
+    const int half = cw >> 2;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const bool leader = (cw == 0 && lane == 0);
+    int i = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++i) {
+      const int bh = t / nc, chunk = t - bh * nc, row0 = bh * n + chunk * C;
+      const uint32_t ph = i & 1;
+      const float sl2 = s[bh % h] * kLog2e;
+      const float lam = exp2f(-sl2);
+      wait_or_fault(&a_done, ph, &dead, kFaultMmaWait);
       tc_fence_after_sync();
-      // S = Q K^T, dS = dO V^T
-      umma_gemm(t0, Operand{smem_u32(sq), C, false}, Operand{smem_u32(sk), C, false}, C, D / 16, false);
-      umma_gemm(t1, Operand{smem_u32(sdo), C, false}, Operand{smem_u32(sv), C, false}, C, E / 16, false);
-    }
-    wait_or_fault(&bar_st, 0, &dead, kFaultTmaWait);
-    if (!dead) {
+      // the previous tile's last store must have read the staging tile before dS_m lands in it
+      if (leader) bulk_wait_read<0>();
+      named_sync(1, 256);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int col0 = half * 64 + cc * 32;
+        masked_store32(t0 + lane_base + col0, sp, row, col0, sl2, lam);    // S_m over the prefix-state tile
+        masked_store32(t1 + lane_base + col0, sds, row, col0, sl2, lam);   // dS_m
+      }
+      const float qd = decay_pow(sl2, row), kd = decay_pow(sl2, C - row);
+#pragma unroll
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int col0 = half * (D / 2) + cc * 32;
+        scale_tmem32(t2 + lane_base + col0, qd);
+        scale_tmem32(t3 + lane_base + col0, kd);
+      }
+      tmem_st_wait();
+      fence_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&sm_ready);
+      wait_or_fault(&b_done, ph, &dead, kFaultMmaWait);
       tc_fence_after_sync();
-      // dQ2 = dO P^T, dK2 = V Dn^T   (state tiles as K-major B operands: rows = d, K = e)
-      umma_gemm(t2, Operand{smem_u32(sdo), C, false}, Operand{smem_u32(sp), D, false}, D, E / 16, false);
-      umma_gemm(t3, Operand{smem_u32(sv), C, false}, Operand{smem_u32(sdn), D, false}, D, E / 16, false);
-      umma_commit(&bar_a);
-    }
-  }
-  __syncwarp();
-  wait_or_fault(&bar_a, 0, &dead, kFaultMmaWait);
-  tc_fence_after_sync();
-  const int row = (warp & 3) * 32 + lane;
-  const int half = warp >> 2;
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+      // epilogue: three output tiles, one after the other through the staging tile
 #pragma unroll
-  for (int cc = 0; cc < 2; ++cc) {
-    const int col0 = half * 64 + cc * 32;
-    masked_store32(t0 + lane_base + col0, sp, row, col0, tab);    // S_m over the prefix-state tile
-    masked_store32(t1 + lane_base + col0, sds, row, col0, tab);   // dS_m
-  }
-  {
-    const float qd = tab[row], kd = tab[C - row];
-#pragma unroll
-    for (int cc = 0; cc < D / 64; ++cc) {
-      const int col0 = half * (D / 2) + cc * 32;
-      scale_tmem32(t2 + lane_base + col0, qd);
-      scale_tmem32(t3 + lane_base + col0, kd);
+      for (int which = 0; which < 3; ++which) {
+        if (which > 0) {
+          if (leader) bulk_wait_read<0>();
+          named_sync(1, 256);
+        }
+        const int width = which < 2 ? D : E;
+        for (int cc = 0; cc < width / 64; ++cc) {
+          const int col0 = half * (width / 2) + cc * 32;
+          if (which == 0) stage_row32(t2 + lane_base + col0, 0xFFFFFFFFu, 0.f, sds, row, col0);
+          else if (which == 1) stage_row32(t3 + lane_base + col0, 0xFFFFFFFFu, 0.f, sds, row, col0);
+          else stage_row32(t0 + lane_base + col0, t1 + lane_base + col0, kd, sds, row, col0);
+        }
+        if (which == 2) {
+          tc_fence_before_sync();
+          mbar_arrive(&t_free);
+        }
+        fence_async_smem();
+        named_sync(1, 256);
+        if (leader) {
+          tma_store_3d(which == 0 ? &map_dq : which == 1 ? &map_dk : &map_dv, sds, 0, row0, 0);
+          bulk_commit();
+        }
+      }
     }
-    tmem_st_wait();
+    if (leader) bulk_wait_all<0>();
   }
-  fence_async_smem();
   tc_fence_before_sync();
   __syncthreads();
-  if (tid == 0 && !dead) {
-    tc_fence_after_sync();
-    // dQ += dS_m K ; dK += dS_m^T Q ; dV1 = S_m^T dO ; dV2 = K Dn
-    umma_gemm(t2, Operand{smem_u32(sds), C, false}, Operand{smem_u32(sk), C, true}, D, C / 16, true);
-    umma_gemm(t3, Operand{smem_u32(sds), C, true}, Operand{smem_u32(sq), C, true}, D, C / 16, true);
-    umma_gemm(t0, Operand{smem_u32(sp), C, true}, Operand{smem_u32(sdo), C, true}, E, C / 16, false);
-    umma_gemm(t1, Operand{smem_u32(sk), C, false}, Operand{smem_u32(sdn), D, true}, E, D / 16, false);
-    umma_commit(&bar_b);
+  if (warp == 2) tmem_dealloc(tmem, 512);
+}
+
+
+// SM count of the current device (cached per device ordinal)
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!cached[dev]) {
+    int v = 0;
+    cached[dev] = (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) ? v : 148;
   }
-  __syncwarp();
-  wait_or_fault(&bar_b, 0, &dead, kFaultMmaWait);
-  tc_fence_after_sync();
-  {
-    const float kd = tab[C - row];
-    __nv_bfloat16* dq_row = DQ + (size_t)(row0 + row) * D;
-    __nv_bfloat16* dk_row = DK + (size_t)(row0 + row) * D;
-    __nv_bfloat16* dv_row = DV + (size_t)(row0 + row) * E;
-#pragma unroll
-    for (int cc = 0; cc < D / 64; ++cc) {
-      const int col0 = half * (D / 2) + cc * 32;
-      store_row32(t2 + lane_base + col0, 0xFFFFFFFFu, 0.f, dq_row, col0);
-      store_row32(t3 + lane_base + col0, 0xFFFFFFFFu, 0.f, dk_row, col0);
-    }
-#pragma unroll
-    for (int cc = 0; cc < E / 64; ++cc) {
-      const int col0 = half * (E / 2) + cc * 32;
-      store_row32(t0 + lane_base + col0, t1 + lane_base + col0, kd, dv_row, col0);
-    }
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
+  return cached[dev];
 }
 
 template <typename F>
@@ -453,8 +572,8 @@ struct Maps {
 };
 
 template <int D, int E>
-cudaError_t launch_chunk_states(const Dims& m, const void* a, const void* bten, const float* s, float* states,
-                                bool backward, cudaStream_t st) {
+cudaError_t launch_chunk_states(const Dims& m, const void* a, const void* bten, const float* s,
+                                __nv_bfloat16* states, bool backward, cudaStream_t st) {
   CUtensorMap ma, mb;
   const uint64_t rows = (uint64_t)m.b * m.h * m.n;
   cudaError_t err = tile_map(&ma, a, rows, D, C, "tensor map (chunk-state A)");
@@ -477,10 +596,13 @@ cudaError_t launch_fwd_output(const Dims& m, const void* q, const void* k, const
   if ((err = tile_map(&mk, k, rows, D, C, "tensor map (k)")) != cudaSuccess) return err;
   if ((err = tile_map(&mv, v, rows, E, C, "tensor map (v)")) != cudaSuccess) return err;
   if ((err = tile_map(&mp, prefix, (uint64_t)m.b * m.h * m.nc * D, E, D, "tensor map (prefix states)")) != cudaSuccess) return err;
-  const size_t smem = (size_t)(C * D + C * E + D * E + C * C) * 2 + 1024;
+  CUtensorMap mo;
+  if ((err = tile_map(&mo, o, rows, E, C, "tensor map (o)")) != cudaSuccess) return err;
+  const size_t smem = (size_t)(C * D + D * E + 2 * C * C + 3 * C * E) * 2 + 1024;
   if ((err = opt_in_smem(k_tc_fwd_output<D, E>, smem)) != cudaSuccess) return err;
-  dim3 grid(m.nc, m.b * m.h);
-  k_tc_fwd_output<D, E><<<grid, 256, smem, st>>>(mq, mk, mv, mp, s, (__nv_bfloat16*)o, m.h, m.n, m.nc);
+  const int tiles = m.nc * m.b * m.h;
+  const int ctas = tiles < sm_count() ? tiles : sm_count();
+  k_tc_fwd_output<D, E><<<ctas, 320, smem, st>>>(mq, mk, mv, mp, mo, s, m.h, m.n, m.nc, tiles);
   return launched("launch of the forward output kernel");
 }
 
@@ -498,13 +620,17 @@ cudaError_t launch_bwd_grads(const Dims& m, const void* q, const void* k, const 
   if ((err = tile_map(&mdo, d_o, rows, E, C, "tensor map (do)")) != cudaSuccess) return err;
   if ((err = tile_map(&mp, prefix, srows, E, D, "tensor map (prefix states)")) != cudaSuccess) return err;
   if ((err = tile_map(&mdn, suffix, srows, E, D, "tensor map (suffix states)")) != cudaSuccess) return err;
+  CUtensorMap mdq, mdk, mdv;
+  if ((err = tile_map(&mdq, dq, rows, D, C, "tensor map (dq)")) != cudaSuccess) return err;
+  if ((err = tile_map(&mdk, dk, rows, D, C, "tensor map (dk)")) != cudaSuccess) return err;
+  if ((err = tile_map(&mdv, dv, rows, E, C, "tensor map (dv)")) != cudaSuccess) return err;
   // Q, K, V, dO, Dn, dS_m, and the larger of P / S_m
   const size_t last = (size_t)(D * E > C * C ? D * E : C * C) * 2;
   const size_t smem = (size_t)(2 * C * D + 2 * C * E + D * E + C * C) * 2 + last + 1024;
   if ((err = opt_in_smem(k_tc_bwd_grads<D, E>, smem)) != cudaSuccess) return err;
-  dim3 grid(m.nc, m.b * m.h);
-  k_tc_bwd_grads<D, E><<<grid, 256, smem, st>>>(mq, mk, mv, mdo, mp, mdn, s, (__nv_bfloat16*)dq, (__nv_bfloat16*)dk,
-                                                (__nv_bfloat16*)dv, m.h, m.n, m.nc);
+  const int tiles = m.nc * m.b * m.h;
+  const int ctas = tiles < sm_count() ? tiles : sm_count();
+  k_tc_bwd_grads<D, E><<<ctas, 320, smem, st>>>(mq, mk, mv, mdo, mp, mdn, mdq, mdk, mdv, s, m.h, m.n, m.nc, tiles);
   return launched("launch of the backward gradient kernel");
 }
 
@@ -515,8 +641,8 @@ bool tensor_path_supported(const Dims& m) {
          (long long)m.b * m.h * m.n < (1LL << 31);
 }
 
-cudaError_t tensor_chunk_states(const Dims& m, const void* a, const void* bten, const float* s, float* states,
-                                bool backward, cudaStream_t st) {
+cudaError_t tensor_chunk_states(const Dims& m, const void* a, const void* bten, const float* s,
+                                __nv_bfloat16* states, bool backward, cudaStream_t st) {
   return launch_chunk_states<128, 128>(m, a, bten, s, states, backward, st);
 }
 
