@@ -187,21 +187,27 @@ def run_ours(args):
 
     plan = engine.make_plan(B, H, N_LOCAL, D, E, dtype)
     graphs = []
-    if sp == 1 and not args.eager:
-        # single device: the six launches of a step go through the C ABI and are
-        # replayed from a CUDA graph, one graph per input set
+    if not args.eager:
+        # the launches of a step (6 kernels; 10 with the two state totals and the two
+        # relay hops of a sequence-parallel rank) go through the C ABI and are replayed
+        # from a CUDA graph, one graph per input set
+        from lasp_b200.pipeline import FixedStep
+        from lasp_b200.utils import get_sequence_parallel_group
+        group = get_sequence_parallel_group() if world > 1 else None
         side = torch.cuda.Stream()
         for q, k, v, do in sets:
-            fw = engine.Forward(plan, q.detach(), k.detach(), v.detach(), s)
-            bw = engine.Backward(plan, q.detach(), k.detach(), v.detach(), do, s, fw.ws)
+            fixed = FixedStep(q.detach(), k.detach(), v.detach(), do, s, group)
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                fw.run(), bw.run()
+                fixed.run()
             torch.cuda.current_stream().wait_stream(side)
+            if world > 1:
+                torch.cuda.synchronize()
+                dist.barrier()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                fw.run(), bw.run()
-            graphs.append((g, fw, bw))
+                fixed.run()
+            graphs.append((g, fixed))
 
     def step(i):
         if graphs:
@@ -278,10 +284,15 @@ def run_ours(args):
     for bw in bws:
         bw.grads()
     torch.cuda.synchronize()
-    reps = max(20, 2 * n_sets)
+    reps = 8 * n_sets
+    kg = torch.cuda.CUDAGraph()     # back-to-back launches of the one kernel, rotating over the input sets
+    with torch.cuda.graph(kg):
+        for i in range(reps):
+            bws[i % n_sets].grads()
+    kg.replay()
+    torch.cuda.synchronize()
     start.record()
-    for i in range(reps):
-        bws[i % n_sets].grads()
+    kg.replay()
     stop.record()
     torch.cuda.synchronize()
     kernel_ms = start.elapsed_time(stop) / reps
@@ -303,11 +314,14 @@ def run_ours(args):
         "config": {"workload": "BASELINE config 1: lightning attention fwd+bwd, b=2/rank, h=12, 2048 tokens/rank, "
                                "d=e=128, decay 2^(-8(i+1)/12)", "parallelism": f"dp{dp}xsp{sp}",
                    "global_batch": B * dp, "global_seq_len": N_LOCAL * sp, "kernel_path": plan.path_name,
-                   "launch": "cuda graph of the 6 C-ABI launches" if graphs else "eager operator calls",
+                   "launch": f"cuda graph of the {graphs[0][1].launches} C-ABI launches" if graphs
+                   else "eager operator calls",
+                   "transport": ("nvlink relay kernel" if graphs else "nccl or nvlink (operator default)")
+                   if world > 1 else "none",
                    "l2": f"inputs rotate over {n_sets} independent sets ({n_sets * set_bytes / 1e6:.0f} MB) > L2"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_steps},
-        "gpu_launches": 6 * args.steps,
+        "gpu_launches": (graphs[0][1].launches if graphs else 6) * args.steps,
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "kernel": f"bwd_grads ({plan.path_name})", "achieved": achieved,
                      "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_kind,

@@ -154,6 +154,54 @@ int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stre
 int lasp_b200_state_combine(int b, int h, int d, int e, int n, const float* s, const float* x_in,
                             const float* x_local, float* x_out, void* stream);
 
+/* ---- state relay over NVLink peer memory ------------------------------ */
+/* total = the rank's own contribution to the outgoing state: the decayed sum of
+ * the local chunk states left in `ws` by lasp_b200_fwd_chunk_states (reverse =
+ * 0) or lasp_b200_bwd_chunk_states (reverse = 1).  Equals kv_out / dkv_out of
+ * the scan phase with a zero incoming state, without touching the chunk states.
+ * Replaces kv[:, :, -1] of lasp/lasp_fuse_parallel.py:941. */
+int lasp_b200_state_total(const lasp_problem* p, const void* ws, size_t ws_bytes, const float* s, float* total,
+                          int reverse, void* stream);
+
+/* The state exchange of a sequence-parallel group as ONE kernel over
+ * peer-mapped buffers.  Rank-to-rank passing,
+ *     x_in(r+1) = exp(-s n) x_in(r) + total(r),
+ * has the closed form x_in(r) = sum_{q<r} exp(-s n)^(r-1-q) total(q); the kernel
+ * stores this rank's `total` into the receive slots of every rank after it in
+ * the chain order (plain peer stores over NVLink) and sums what the ranks before
+ * it stored here.  Replaces dist.recv / KV update / dist.send of
+ * lasp/lasp_fuse_parallel.py:1095-1106 (forward) and :1129-1135 (backward: the
+ * caller reverses the chain order) - one NVLink latency instead of ranks-1.
+ * `position` is this rank's place in the chain order (0 sends only, ranks-1
+ * receives only); peer_* arrays are indexed by position.  All pointers are
+ * device pointers; peer_* point into other GPUs' memory mapped into this
+ * process (a symmetric allocation, zeroed once).  Per rank and direction:
+ *   slots   : 2 x ranks x (b*h*d*e) 8-byte words {value, step}
+ *             [step parity][source][element]; a word is valid for the current
+ *             step when its second half equals the step number, so no flag or
+ *             fence is needed on the path
+ *   acks    : ranks x 8 words, 128 bytes apart  [destination][slice], written by destinations
+ *   counters: 16 words, zeroed once; the kernel keeps the step number there, so
+ *             a replayed CUDA graph needs no new arguments.
+ * Waits give up after wait_clocks GPU clocks (0 = about two seconds) and set
+ * bit 4 of the fault word (lasp_b200_read_status). */
+typedef struct {
+  int32_t b, h, d, e, n;     /* state shape and the rank's local sequence length */
+  int32_t ranks;             /* group size, 2..8 */
+  int32_t position;          /* this rank's place in the chain order */
+  int32_t reserved;
+  const float* s;            /* h decay rates */
+  const float* total;        /* (b,h,d,e) fp32 from lasp_b200_state_total */
+  float* x_in;               /* (b,h,d,e) fp32 out: the incoming state; NULL when position == 0 */
+  const void* my_slots;      /* local receive slots */
+  const uint32_t* my_acks;   /* local acknowledgement words */
+  uint32_t* counters;        /* local */
+  void* peer_slots[8];       /* receive slots of each position (entries > position are written) */
+  uint32_t* peer_acks[8];    /* acknowledgement words of each position (entries < position are written) */
+  int64_t wait_clocks;
+} lasp_exchange_args;
+int lasp_b200_state_exchange(const lasp_exchange_args* a, void* stream);
+
 /* Copies this device's sticky kernel-fault word to *status_host (synchronises
  * the stream) and clears it when clear != 0.  0 = no kernel reported a fault;
  * the tensor-core kernels set bits when one of their bounded waits (TMA

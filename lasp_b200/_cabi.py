@@ -48,6 +48,12 @@ class BwdArgs(C.Structure):
                 ("ws", C.c_void_p), ("ws_bytes", C.c_size_t)]
 
 
+class ExchangeArgs(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("b", "h", "d", "e", "n", "ranks", "position", "reserved")] + \
+               [(n, C.c_void_p) for n in ("s", "total", "x_in", "my_slots", "my_acks", "counters")] + \
+               [("peer_slots", C.c_void_p * 8), ("peer_acks", C.c_void_p * 8), ("wait_clocks", C.c_int64)]
+
+
 _PP, _FP, _BP = C.POINTER(Problem), C.POINTER(FwdArgs), C.POINTER(BwdArgs)
 
 # symbol -> (restype, argtypes); every entry point include/lasp_b200.h declares
@@ -70,6 +76,8 @@ SIGNATURES = {
     "lasp_b200_state_combine": (C.c_int, [C.c_int] * 5 + [C.c_void_p] * 5),
     "lasp_b200_read_status": (C.c_int, [C.POINTER(C.c_int32), C.c_int, C.c_void_p]),
     "lasp_b200_forward_static": (C.c_int, [_PP, _FP, C.c_void_p]),
+    "lasp_b200_state_total": (C.c_int, [_PP, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "lasp_b200_state_exchange": (C.c_int, [C.POINTER(ExchangeArgs), C.c_void_p]),
 }
 STATIC_SCRATCH_BYTES = 64 << 20  # LASP_B200_STATIC_SCRATCH_BYTES
 

@@ -119,8 +119,20 @@ class SequenceParallelAttention(torch.autograd.Function):
         link = comm.StateLink(group)
 
         plan = _plan_for(q, v)
-        fw = ENGINE.Forward(plan, q, k, v, s, kv_in=KV if rank > 0 else None, kv_out=KV if rank < last else None)
-        if overlap:
+        relay = comm.relay_for(group, KV.numel(), q.device) if (overlap and last > 0 and q.is_cuda) else None
+        if relay is not None:
+            # chunk states -> own total -> one exchange kernel (push to later ranks, gather from earlier) -> scan -> outputs
+            fw = ENGINE.Forward(plan, q, k, v, s, kv_in=KV if rank > 0 else None, kv_out=None)
+            fw.chunk_states()
+            total = ENGINE.state_total(plan, fw.ws, s, reverse=False)
+            relay.exchange(total, KV if rank > 0 else None, s, n, backward=False)
+            fw.scan()
+            fw.output()
+        else:
+            fw = ENGINE.Forward(plan, q, k, v, s, kv_in=KV if rank > 0 else None, kv_out=KV if rank < last else None)
+        if relay is not None:
+            pass
+        elif overlap:
             pending = link.post_recv(KV, prev_rank) if rank > 0 else None
             fw.chunk_states()
             link.wait(pending)
@@ -136,7 +148,7 @@ class SequenceParallelAttention(torch.autograd.Function):
                 link.send(KV, next_rank)
 
         ctx.plan, ctx.fwd_ws, ctx.DKV, ctx.overlap = plan, fw.ws, DKV, overlap
-        ctx.link, ctx.rank, ctx.last = link, rank, last
+        ctx.link, ctx.rank, ctx.last, ctx.relay = link, rank, last, relay
         ctx.prev_rank, ctx.next_rank = prev_rank, next_rank
         ctx.save_for_backward(q, k, v, s)
         return fw.o
@@ -145,6 +157,15 @@ class SequenceParallelAttention(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, s = ctx.saved_tensors
         DKV, link, rank, last = ctx.DKV, ctx.link, ctx.rank, ctx.last
+        if ctx.relay is not None:
+            bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws,
+                                 dkv_in=DKV if rank < last else None, dkv_out=None)
+            bw.chunk_states()
+            total = ENGINE.state_total(ctx.plan, bw.ws, s, reverse=True)
+            ctx.relay.exchange(total, DKV if rank < last else None, s, q.shape[2], backward=True)
+            bw.scan()
+            bw.grads()
+            return bw.dq, bw.dk, bw.dv, None, None, None, None
         bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws,
                              dkv_in=DKV if rank < last else None, dkv_out=DKV if rank > 0 else None)
         if ctx.overlap:

@@ -12,6 +12,9 @@ same calls degrade to isend/irecv plus ``wait()``.
 """
 from __future__ import annotations
 
+import os
+import warnings
+
 import torch
 import torch.distributed as dist
 
@@ -77,3 +80,93 @@ class StateLink:
 
     def send(self, buf: torch.Tensor, dst: int) -> None:
         dist.send(buf, dst=dst, group=self.group)
+
+
+# ---------------------------------------------------------------------------
+# NVLink exchange: the whole state exchange as one kernel over peer-mapped buffers
+# ---------------------------------------------------------------------------
+class NvlinkExchange:
+    """Peer-mapped receive slots, flags and acknowledgement words of one
+    sequence-parallel group for one state size, and the launcher of the
+    exchange kernel (``lasp_b200_state_exchange``).
+
+    The buffers come from torch's symmetric-memory allocator (a CUDA virtual
+    memory allocation exported to the group's other ranks); the transfer itself
+    is done by the library's own kernel with plain peer stores - no NCCL call
+    is on the path, so a whole forward or backward can be captured in a CUDA
+    graph.  Each rank's buffer holds two regions (forward, backward), each:
+        [0, 8K) acks [destination][slice]   [8K, 9K) counters
+        [32K, ...) slots [parity][source][element] of 8-byte {value, step} words
+    """
+    MAX_RANKS = 8
+    _HEADER = 32768
+
+    def __init__(self, group, elems: int, device):
+        import torch.distributed._symmetric_memory as symm
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer stores only
+        self.group, self.elems, self.device = group, elems, torch.device(device)
+        self.rank = dist.get_rank(group)
+        self.size = dist.get_world_size(group)
+        if self.size > self.MAX_RANKS:
+            raise RuntimeError(f"the peer-mapped exchange handles groups of up to {self.MAX_RANKS} ranks")
+        self.region = self._HEADER + 2 * self.size * elems * 8
+        self.buf = symm.empty(2 * self.region // 4, dtype=torch.float32, device=self.device)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)   # every rank has zeroed its flags before any peer writes one
+
+    def exchange(self, total, x_in, s, n: int, backward: bool, wait_clocks: int = 0) -> None:
+        """Launch the exchange on the current stream.  Forward: states flow towards
+        higher ranks; backward: towards lower ranks.  ``x_in`` (b,h,d,e) receives the
+        incoming state; it is None on the rank that has nobody before it."""
+        from . import _cabi, engine
+        b, h, d, e = total.shape
+        assert b * h * d * e == self.elems
+        pos = self.size - 1 - self.rank if backward else self.rank
+        assert (x_in is not None) == (pos > 0)
+        off = self.region if backward else 0
+        sl = s.reshape(-1).to(device=total.device, dtype=torch.float32).contiguous()
+        a = _cabi.ExchangeArgs()
+        a.b, a.h, a.d, a.e, a.n, a.ranks, a.position = b, h, d, e, n, self.size, pos
+        a.s, a.total = sl.data_ptr(), total.data_ptr()
+        a.x_in = x_in.data_ptr() if x_in is not None else None
+        me = self.ptrs[self.rank] + off
+        a.my_acks, a.counters, a.my_slots = me, me + 8192, me + self._HEADER
+        for q in range(self.size):
+            base = self.ptrs[self.size - 1 - q if backward else q] + off   # buffer of the rank at position q
+            a.peer_acks[q], a.peer_slots[q] = base, base + self._HEADER
+        a.wait_clocks = wait_clocks
+        engine.state_exchange(a, total.device)
+        self._keep = (sl, total, x_in)   # alive until the next launch is enqueued on the same stream
+
+
+_relays = {}
+_relay_unavailable = False
+
+
+def transport() -> str:
+    """'nvlink' (the library's exchange kernel over peer memory) or 'nccl'
+    (rank-to-rank isend/irecv); env LASP_B200_TRANSPORT, default 'auto' = nvlink
+    when the group's buffers can be peer-mapped."""
+    return os.environ.get("LASP_B200_TRANSPORT", "auto")
+
+
+def relay_for(group, elems: int, device):
+    """The group's NvlinkExchange for this state size, or None when peer mapping
+    is not available (collective: every rank of the group must call it alike)."""
+    global _relay_unavailable
+    if transport() == "nccl" or _relay_unavailable:
+        return None
+    key = (id(group), elems, torch.device(device).index)
+    if key not in _relays:
+        try:
+            _relays[key] = NvlinkExchange(group, elems, device)
+        except Exception as exc:  # noqa: BLE001
+            if transport() == "nvlink":
+                raise
+            warnings.warn(f"lasp_b200: peer-mapped state exchange unavailable ({exc}); using NCCL send/recv")
+            _relay_unavailable = True
+            return None
+    return _relays[key]

@@ -225,6 +225,33 @@ int lasp_b200_state_combine(int b, int h, int d, int e, int n, const float* s, c
   return cuda_fail(lasp::state_combine(b, h, d, e, n, s, x_in, x_local, x_out, static_cast<cudaStream_t>(stream)));
 }
 
+int lasp_b200_state_total(const lasp_problem* p, const void* ws, size_t ws_bytes, const float* s, float* total,
+                          int reverse, void* stream) {
+  lasp::Dims m;
+  int st = make_dims(p, &m);
+  if (st != LASP_OK) return st;
+  if (!ws || !s || !total) return LASP_ERR_NULL;
+  if (!aligned16(ws) || !aligned16(total)) return LASP_ERR_ALIGN;
+  if (ws_bytes < workspace_bytes(m)) return LASP_ERR_WORKSPACE;
+  return cuda_fail(lasp::state_total(m, s, ws, total, reverse != 0, static_cast<cudaStream_t>(stream)));
+}
+
+int lasp_b200_state_exchange(const lasp_exchange_args* a, void* stream) {
+  if (!a || !a->s || !a->total || !a->counters) return LASP_ERR_NULL;
+  bind_context_once();
+  if (a->b <= 0 || a->h <= 0 || a->d <= 0 || a->e <= 0 || a->n <= 0 || (a->d * a->e) % 4) return LASP_ERR_SHAPE;
+  if (a->ranks < 2 || a->ranks > 8 || a->position < 0 || a->position >= a->ranks) return LASP_ERR_SHAPE;
+  if ((a->position > 0) != (a->x_in != nullptr)) return LASP_ERR_NULL;
+  if (a->position > 0 && !a->my_slots) return LASP_ERR_NULL;
+  if (a->position < a->ranks - 1 && !a->my_acks) return LASP_ERR_NULL;
+  for (int q = 0; q < a->ranks; ++q) {
+    if (q < a->position && !a->peer_acks[q]) return LASP_ERR_NULL;
+    if (q > a->position && !a->peer_slots[q]) return LASP_ERR_NULL;
+  }
+  if (!aligned16(a->total) || !aligned16(a->x_in) || !aligned16(a->my_slots)) return LASP_ERR_ALIGN;
+  return cuda_fail(lasp::state_exchange(*a, static_cast<cudaStream_t>(stream)));
+}
+
 int lasp_b200_read_status(int32_t* status_host, int clear, void* stream) {
   if (!status_host) return LASP_ERR_NULL;
   return cuda_fail(lasp::read_fault_word(status_host, clear != 0, static_cast<cudaStream_t>(stream)));

@@ -48,8 +48,11 @@ enum : int32_t {
   kFaultNone = 0,
   kFaultTmaWait = 1,   // a bounded wait on a TMA mbarrier ran out
   kFaultMmaWait = 2,   // a bounded wait on a tcgen05.commit mbarrier ran out
+  kFaultRelayWait = 4, // a bounded wait on a peer's flag ran out (state relay)
 };
 cudaError_t read_fault_word(int32_t* host, bool clear, cudaStream_t st);
+// device address of the current device's fault word (for kernels in other translation units)
+cudaError_t fault_word_address(int32_t** out);
 
 // name of the host-side step that produced the last cudaError_t (for error text)
 extern thread_local const char* g_failed_step;
@@ -68,6 +71,11 @@ cudaError_t simt_bwd_grads(const Dims& m, const void* q, const void* k, const vo
                            void* dv, cudaStream_t st);
 cudaError_t state_combine(int b, int h, int d, int e, int n, const float* s, const float* x_in,
                           const float* x_local, float* x_out, cudaStream_t st);
+
+// state relay (relay_kernels.cu)
+cudaError_t state_total(const Dims& m, const float* s, const void* local, float* total, bool reverse,
+                        cudaStream_t st);
+cudaError_t state_exchange(const lasp_exchange_args& a, cudaStream_t st);
 
 // tcgen05 path (tensor_kernels.cu)
 cudaError_t tensor_chunk_states(const Dims& m, const void* a, const void* bten, const float* s,

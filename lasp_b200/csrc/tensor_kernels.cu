@@ -30,6 +30,21 @@ cudaError_t read_fault_word(int32_t* host, bool clear, cudaStream_t st) {
   return cudaStreamSynchronize(st);
 }
 
+cudaError_t fault_word_address(int32_t** out) {
+  static int32_t* cached[64] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!cached[dev]) {
+    void* p = nullptr;
+    if ((err = cudaGetSymbolAddress(&p, g_fault_word)) != cudaSuccess) return err;
+    cached[dev] = static_cast<int32_t*>(p);
+  }
+  *out = cached[dev];
+  return cudaSuccess;
+}
+
 namespace {
 
 using namespace sm100;

@@ -176,6 +176,24 @@ def state_combine(s, x_in, x_local, n: int, out=None):
     return out
 
 
+def state_total(plan: Plan, ws: torch.Tensor, s, reverse: bool, out=None):
+    """This rank's own contribution to the outgoing state, from the local chunk
+    states in ``ws`` (after the chunk-state phase, before the scan)."""
+    _require_cuda(ws)
+    out = out if out is not None else torch.empty(plan.b, plan.h, plan.d, plan.e, dtype=torch.float32,
+                                                  device=ws.device)
+    sl = _slopes(s, plan.h, ws.device)
+    with _on_device(ws.device):
+        _cabi.call("lasp_b200_state_total", C.byref(plan.problem), _ptr(ws), ws.numel(), _ptr(sl), _ptr(out),
+                   1 if reverse else 0, _stream())
+    return out
+
+
+def state_exchange(args: "_cabi.ExchangeArgs", device) -> None:
+    with _on_device(device):
+        _cabi.call("lasp_b200_state_exchange", C.byref(args), _stream())
+
+
 def read_status(clear: bool = True) -> int:
     """Sticky kernel-fault word of the current device (synchronises)."""
     word = C.c_int32(0)
