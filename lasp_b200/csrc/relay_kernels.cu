@@ -21,10 +21,13 @@
 // Every wait is bounded: when it runs out the kernel sets kFaultRelayWait in the
 // fault word and carries on (its output is then meaningless).
 #include "common.cuh"
+#include "exchange_layout.h"
 
 namespace lasp {
 
 namespace {
+
+using namespace xl;
 
 __device__ __forceinline__ uint32_t ld_volatile(const uint32_t* p) {
   uint32_t v;
@@ -55,12 +58,6 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, l
   return true;
 }
 
-constexpr int kMaxRanks = 8;
-constexpr int kSlices = 8;        // independently acknowledged slices of a state
-constexpr int kGatherCtas = 16;   // CTAs per slice on the gathering side
-constexpr int kPushTarget = 128;  // CTAs on the pushing side, shared among (destination, slice) pairs
-constexpr int kFlagStride = 32;   // acknowledgement words sit 128 bytes apart
-
 struct ExchangeParams {
   const float* total;           // local (b,h,d,e): this rank's own contribution
   float* x_in;                  // local (b,h,d,e) out: the incoming state (NULL: no sender before me)
@@ -84,22 +81,20 @@ struct ExchangeParams {
 __global__ void __launch_bounds__(256) k_state_exchange(const ExchangeParams p) {
   const uint32_t step = p.counters[0] + 1;
   const int parity = step & 1;
-  const long long per = ((p.elems / 4 + kSlices - 1) / kSlices) * 4;  // floats per slice
-  const int push_ctas = p.n_dst * kSlices * p.push_parts;
-  if ((int)blockIdx.x < push_ctas) {
+  const int n_push = push_ctas(p.n_dst);
+  if ((int)blockIdx.x < n_push) {
     // ---- push: my total -> slot [parity][me] of one destination, one slice part
-    const int part = blockIdx.x % p.push_parts, slice = (blockIdx.x / p.push_parts) % kSlices;
-    const int dst = p.me + 1 + blockIdx.x / (p.push_parts * kSlices);
-    const long long slo = (long long)slice * per, shi = slo + per < p.elems ? slo + per : p.elems;
-    const long long sub = ((per / 4 + p.push_parts - 1) / p.push_parts) * 4;
-    const long long lo = slo + (long long)part * sub, hi = lo + sub < shi ? lo + sub : shi;
-    if (threadIdx.x == 0 && step >= 3) {
+    int di, slice, part;
+    push_decode(blockIdx.x, p.push_parts, &di, &slice, &part);
+    const int dst = p.me + 1 + di;
+    long long lo, hi;
+    part_bounds(p.elems, slice, p.push_parts, part, &lo, &hi);
+    if (threadIdx.x == 0 && needs_ack_wait(step)) {
       // the slot was last used two steps ago: its reader must have acknowledged it
-      if (!wait_flag(p.my_acks + (dst * kSlices + slice) * kFlagStride, step - 2, p.wait_clocks))
-        atomicOr(p.fault, kFaultRelayWait);
+      if (!wait_flag(p.my_acks + ack_index(dst, slice), step - 2, p.wait_clocks)) atomicOr(p.fault, kFaultRelayWait);
     }
     __syncthreads();
-    uint2* out = p.dst_slots[dst] + ((long long)parity * p.ranks + p.me) * p.elems;
+    uint2* out = p.dst_slots[dst] + slot_offset(parity, p.ranks, p.me, p.elems);
     constexpr int kUnroll = 4;
     for (long long base = lo + (long long)threadIdx.x * 4; base < hi; base += 256 * 4 * kUnroll) {
       float4 t[kUnroll];
@@ -119,12 +114,11 @@ __global__ void __launch_bounds__(256) k_state_exchange(const ExchangeParams p) 
     }
   } else if (p.x_in) {
     // ---- gather: x_in = sum_{q < me} a^(me-1-q) slot[parity][q], each word awaited until it carries `step`
-    const int gi = blockIdx.x - push_ctas;
-    const int part = gi % kGatherCtas, slice = gi / kGatherCtas;
-    const long long slo = (long long)slice * per, shi = slo + per < p.elems ? slo + per : p.elems;
-    const long long sub = ((per / 4 + kGatherCtas - 1) / kGatherCtas) * 4;
-    const long long lo = slo + (long long)part * sub, hi = lo + sub < shi ? lo + sub : shi;
-    const uint2* slots = p.my_slots + (long long)parity * p.ranks * p.elems;
+    int slice, part;
+    gather_decode(blockIdx.x - n_push, &slice, &part);
+    long long lo, hi;
+    part_bounds(p.elems, slice, kGatherCtas, part, &lo, &hi);
+    const uint2* slots = p.my_slots + slot_offset(parity, p.ranks, 0, p.elems);
     bool late = false;
     for (long long el = lo + (long long)threadIdx.x * 4; el < hi; el += 256 * 4) {
       const float a = expf(-p.s[(el / p.de) % p.h] * (float)p.n);
@@ -140,8 +134,8 @@ __global__ void __launch_bounds__(256) k_state_exchange(const ExchangeParams p) 
 #pragma unroll
       for (int q = 0; q < kMaxRanks; ++q) {   // Horner: acc = a * acc + slot[q]
         if (q < p.n_src) {
-          if (w0[q].y != step || w0[q].w != step || w1[q].y != step || w1[q].w != step) {
-            const long long t0 = clock64();
+          if (!late && (w0[q].y != step || w0[q].w != step || w1[q].y != step || w1[q].w != step)) {
+            const long long t0 = clock64();  // after one wait has run out this thread waits no more
             do {
               w0[q] = ld_volatile_v4(slots + (long long)q * p.elems + el);
               w1[q] = ld_volatile_v4(slots + (long long)q * p.elems + el + 2);
@@ -165,7 +159,7 @@ __global__ void __launch_bounds__(256) k_state_exchange(const ExchangeParams p) 
     if (threadIdx.x == 0) {
       if (atomicAdd(&p.counters[2 + slice], 1u) == (uint32_t)(kGatherCtas - 1)) {
         p.counters[2 + slice] = 0;
-        for (int q = 0; q < p.n_src; ++q) st_volatile(p.src_acks[q] + (p.me * kSlices + slice) * kFlagStride, step);
+        for (int q = 0; q < p.n_src; ++q) st_volatile(p.src_acks[q] + ack_index(p.me, slice), step);
       }
     }
   }
@@ -264,9 +258,8 @@ cudaError_t state_exchange(const lasp_exchange_args& a, cudaStream_t st) {
   p.n = a.n;
   p.elems = (long long)a.b * a.h * a.d * a.e;
   p.wait_clocks = a.wait_clocks > 0 ? a.wait_clocks : 4000000000LL;  // about two seconds
-  p.push_parts = 1;
-  if (p.n_dst > 0 && kPushTarget / (p.n_dst * kSlices) > 1) p.push_parts = kPushTarget / (p.n_dst * kSlices);
-  const int ctas = p.n_dst * kSlices * p.push_parts + (p.n_src > 0 ? kSlices * kGatherCtas : 0);
+  p.push_parts = push_parts(p.n_dst);
+  const int ctas = push_ctas(p.n_dst) + gather_ctas(p.n_src);
   if (ctas == 0) return cudaSuccess;
   k_state_exchange<<<ctas, 256, 0, st>>>(p);
   return cudaGetLastError();

@@ -55,6 +55,7 @@ def _worker(rank, world, port, mode, params, errq):
     try:
         os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
         os.environ["LASP_B200_TRANSPORT"] = params.get("transport", "auto")
+        torch.set_num_threads(max(1, (os.cpu_count() or 8) // world))   # the ranks share the host cores
         torch.cuda.set_device(rank)
         dev = torch.device("cuda", rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -65,14 +66,25 @@ def _worker(rank, world, port, mode, params, errq):
         initialize_lasp(p["dp"], p["sp"])
         dp_rank, sp_rank = rank // p["sp"], rank % p["sp"]
         dtype = getattr(torch, p["dtype"])
+        s = slopes_for(p["slopes"], p["h"])
         if mode == "golden":
             q, k, v, do = O.make_inputs(p["seed"], p["b"], p["h"], p["n"], p["d"], p["e"])
-        else:  # large global tensors: torch's generator is much faster and identical on every rank
-            g = torch.Generator().manual_seed(p["seed"])
-            q, k = (torch.randn(p["b"], p["h"], p["n"], p["d"], generator=g) * p["d"] ** -0.5 for _ in range(2))
-            v, do = (torch.randn(p["b"], p["h"], p["n"], p["e"], generator=g) for _ in range(2))
-        s = slopes_for(p["slopes"], p["h"])
-        qi, ki, vi, doi = (split(t.to(dtype), p["dp"], p["sp"], dp_rank, sp_rank).to(dev) for t in (q, k, v, do))
+            qi, ki, vi, doi = (split(t.to(dtype), p["dp"], p["sp"], dp_rank, sp_rank).to(dev) for t in (q, k, v, do))
+        else:
+            # The global tensors are defined piecewise - one seeded draw per (tensor, global batch row,
+            # sequence-parallel chunk) - so that a rank only generates its own chunk plus, for the oracle,
+            # the checked heads of its batch rows.
+            nl, bl = p["n"] // p["sp"], p["b"] // p["dp"]
+
+            def piece(which, b_global, chunk):
+                g = torch.Generator().manual_seed(((p["seed"] * 4 + which) * 4096 + b_global) * 64 + chunk)
+                width = p["d"] if which < 2 else p["e"]
+                t = torch.randn(p["h"], nl, width, generator=g)
+                return t * p["d"] ** -0.5 if which < 2 else t
+
+            rows = [i * p["dp"] + dp_rank for i in range(bl)]   # batch interleaved over dp
+            qi, ki, vi, doi = (torch.stack([piece(w, bg, sp_rank) for bg in rows]).to(dtype).to(dev)
+                               for w in range(4))
         got = _run_variants(lasp, qi, ki, vi, doi, s.to(dev))
         if mode == "golden":
             g = load_golden(p["name"])
@@ -85,9 +97,8 @@ def _worker(rank, world, port, mode, params, errq):
         else:
             # oracle rank chain on this rank's batch slice, a few heads only (heads are independent)
             heads = p["check_heads"]
-            cast = (lambda t: t.to(dtype).float())
-            gq, gk, gv, gdo = (torch.cat([split(cast(t), p["dp"], p["sp"], dp_rank, r) for r in range(p["sp"])], 2)
-                               [:, heads] for t in (q, k, v, do))
+            gq, gk, gv, gdo = (torch.stack([torch.cat([piece(w, bg, r)[heads] for r in range(p["sp"])], 1)
+                                            for bg in rows]).to(dtype).float() for w in range(4))
             outs, grads, _ = O.sp_chain(gq, gk, gv, s[heads], gdo, p["sp"])
             ref = dict(o=outs[sp_rank], dq=grads[sp_rank][0], dk=grads[sp_rank][1], dv=grads[sp_rank][2])
             tol = TOL_BF16 if dtype != torch.float32 else TOL_FP32
