@@ -96,11 +96,18 @@ class SequenceParallelAttention(torch.autograd.Function):
     lasp/lasp_fuse_parallel.py:1073-1137).
 
     Each rank holds one contiguous chunk of the sequence.  Forward: the KV
-    state arrives from the previous rank, the outgoing state leaves for the
-    next; backward: dKV travels the other way.  ``overlap`` chooses between the
-    reference's order (receive, compute, send) and the overlapped one (post the
-    receive, run the state-independent chunk-state kernel, wait, scan, send,
-    then the output kernel).
+    state arrives from the ranks before, the outgoing state leaves for the
+    ranks after; backward: dKV travels the other way.  Three schedules:
+
+    * ``overlap=False`` (lasp_naive, lasp_cache): the reference's order -
+      blocking receive, all three kernels, blocking send (NCCL / gloo).
+    * ``overlap=True`` with the peer-mapped exchange (the default on GPUs of
+      one node): chunk-state kernel -> this rank's total -> ONE exchange kernel
+      that stores the total into every later rank's memory over NVLink and
+      sums what earlier ranks stored here -> scan -> output kernel.
+    * ``overlap=True`` over NCCL (LASP_B200_TRANSPORT=nccl, or CPU tensors):
+      post the receive, run the state-independent chunk-state kernel, wait,
+      scan, post the send, run the output kernel.
     """
 
     @staticmethod
@@ -117,38 +124,36 @@ class SequenceParallelAttention(torch.autograd.Function):
         last = get_sequence_parallel_world_size() - 1
         prev_rank, next_rank = get_seq_parallel_send_rank(), get_seq_parallel_receive_rank()
         link = comm.StateLink(group)
-
         plan = _plan_for(q, v)
-        relay = comm.relay_for(group, KV.numel(), q.device) if (overlap and last > 0 and q.is_cuda) else None
-        if relay is not None:
-            # chunk states -> own total -> one exchange kernel (push to later ranks, gather from earlier) -> scan -> outputs
-            fw = ENGINE.Forward(plan, q, k, v, s, kv_in=KV if rank > 0 else None, kv_out=None)
+        kv_in = KV if rank > 0 else None
+        exchange = comm.relay_for(group, KV.numel(), q.device) if (overlap and last > 0 and q.is_cuda) else None
+
+        if exchange is not None:
+            fw = ENGINE.Forward(plan, q, k, v, s, kv_in=kv_in, kv_out=None)
             fw.chunk_states()
             total = ENGINE.state_total(plan, fw.ws, s, reverse=False)
-            relay.exchange(total, KV if rank > 0 else None, s, n, backward=False)
+            exchange.exchange(total, kv_in, s, n, backward=False)
             fw.scan()
             fw.output()
         else:
-            fw = ENGINE.Forward(plan, q, k, v, s, kv_in=KV if rank > 0 else None, kv_out=KV if rank < last else None)
-        if relay is not None:
-            pass
-        elif overlap:
-            pending = link.post_recv(KV, prev_rank) if rank > 0 else None
-            fw.chunk_states()
-            link.wait(pending)
-            fw.scan()
-            sent = link.post_send(KV, next_rank) if rank < last else None
-            fw.output()
-            link.wait(sent)
-        else:
-            if rank > 0:
-                link.recv(KV, prev_rank)
-            fw.run()
-            if rank < last:
-                link.send(KV, next_rank)
+            fw = ENGINE.Forward(plan, q, k, v, s, kv_in=kv_in, kv_out=KV if rank < last else None)
+            if overlap:
+                pending = link.post_recv(KV, prev_rank) if rank > 0 else None
+                fw.chunk_states()
+                link.wait(pending)
+                fw.scan()
+                sent = link.post_send(KV, next_rank) if rank < last else None
+                fw.output()
+                link.wait(sent)
+            else:
+                if rank > 0:
+                    link.recv(KV, prev_rank)
+                fw.run()
+                if rank < last:
+                    link.send(KV, next_rank)
 
         ctx.plan, ctx.fwd_ws, ctx.DKV, ctx.overlap = plan, fw.ws, DKV, overlap
-        ctx.link, ctx.rank, ctx.last, ctx.relay = link, rank, last, relay
+        ctx.link, ctx.rank, ctx.last, ctx.exchange = link, rank, last, exchange
         ctx.prev_rank, ctx.next_rank = prev_rank, next_rank
         ctx.save_for_backward(q, k, v, s)
         return fw.o
@@ -157,17 +162,17 @@ class SequenceParallelAttention(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, s = ctx.saved_tensors
         DKV, link, rank, last = ctx.DKV, ctx.link, ctx.rank, ctx.last
-        if ctx.relay is not None:
-            bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws,
-                                 dkv_in=DKV if rank < last else None, dkv_out=None)
+        dkv_in = DKV if rank < last else None
+        if ctx.exchange is not None:
+            bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws, dkv_in=dkv_in, dkv_out=None)
             bw.chunk_states()
             total = ENGINE.state_total(ctx.plan, bw.ws, s, reverse=True)
-            ctx.relay.exchange(total, DKV if rank < last else None, s, q.shape[2], backward=True)
+            ctx.exchange.exchange(total, dkv_in, s, q.shape[2], backward=True)
             bw.scan()
             bw.grads()
             return bw.dq, bw.dk, bw.dv, None, None, None, None
-        bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws,
-                             dkv_in=DKV if rank < last else None, dkv_out=DKV if rank > 0 else None)
+        bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws, dkv_in=dkv_in,
+                             dkv_out=DKV if rank > 0 else None)
         if ctx.overlap:
             pending = link.post_recv(DKV, ctx.next_rank) if rank < last else None
             bw.chunk_states()

@@ -651,25 +651,52 @@ cudaError_t launch_bwd_grads(const Dims& m, const void* q, const void* k, const 
 
 }  // namespace
 
-bool tensor_path_supported(const Dims& m) {
-  return m.dtype == LASP_BF16 && m.d == 128 && m.e == 128 && m.n % C == 0 &&
-         (long long)m.b * m.h * m.n < (1LL << 31);
+// d = e = 128 is verified against the oracle on B200.  The 64-wide
+// instantiations are built but only selected when LASP_B200_TENSOR_HEAD64=1
+// until they have had the same verification.
+static bool head64_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("LASP_B200_TENSOR_HEAD64");
+    return v && v[0] == '1';
+  }();
+  return on;
 }
+
+bool tensor_path_supported(const Dims& m) {
+  const bool dims_ok = (m.d == 128 && m.e == 128) ||
+                       (head64_enabled() && (m.d == 64 || m.d == 128) && (m.e == 64 || m.e == 128));
+  return m.dtype == LASP_BF16 && dims_ok && m.n % C == 0 && (long long)m.b * m.h * m.n < (1LL << 31);
+}
+
+#define LASP_DISPATCH_DE(m, CALL)                                        \
+  do {                                                                    \
+    if ((m).d == 128 && (m).e == 128) return CALL(128, 128);              \
+    if ((m).d == 128 && (m).e == 64) return CALL(128, 64);                \
+    if ((m).d == 64 && (m).e == 128) return CALL(64, 128);                \
+    if ((m).d == 64 && (m).e == 64) return CALL(64, 64);                  \
+    return cudaErrorInvalidValue;                                         \
+  } while (0)
 
 cudaError_t tensor_chunk_states(const Dims& m, const void* a, const void* bten, const float* s,
                                 __nv_bfloat16* states, bool backward, cudaStream_t st) {
-  return launch_chunk_states<128, 128>(m, a, bten, s, states, backward, st);
+#define LASP_CALL(DD, EE) launch_chunk_states<DD, EE>(m, a, bten, s, states, backward, st)
+  LASP_DISPATCH_DE(m, LASP_CALL);
+#undef LASP_CALL
 }
 
 cudaError_t tensor_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
                               const __nv_bfloat16* prefix, void* o, cudaStream_t st) {
-  return launch_fwd_output<128, 128>(m, q, k, v, s, prefix, o, st);
+#define LASP_CALL(DD, EE) launch_fwd_output<DD, EE>(m, q, k, v, s, prefix, o, st)
+  LASP_DISPATCH_DE(m, LASP_CALL);
+#undef LASP_CALL
 }
 
 cudaError_t tensor_bwd_grads(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
                              const float* s, const __nv_bfloat16* prefix, const __nv_bfloat16* suffix, void* dq,
                              void* dk, void* dv, cudaStream_t st) {
-  return launch_bwd_grads<128, 128>(m, q, k, v, d_o, s, prefix, suffix, dq, dk, dv, st);
+#define LASP_CALL(DD, EE) launch_bwd_grads<DD, EE>(m, q, k, v, d_o, s, prefix, suffix, dq, dk, dv, st)
+  LASP_DISPATCH_DE(m, LASP_CALL);
+#undef LASP_CALL
 }
 
 }  // namespace lasp

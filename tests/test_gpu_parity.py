@@ -264,3 +264,45 @@ def test_tensor_path_outgoing_states():
     e1, e2 = O.max_rel_err(kv_out, kv_ref), O.max_rel_err(dkv_out, dkv_ref)
     print("outgoing state errors", e1, e2)
     assert e1 < 1e-2 and e2 < 1e-2
+
+
+def test_tensor_long_sequence_tnl1b_slice():
+    # TNL-1B attention shape (h=16, d=e=128, b=1), one rank's share at SP=8 of a 131072-token sequence
+    b, h, n, d, e = 1, 16, 16384, 128, 128
+    q, k, v, do = O.make_inputs(91, b, h, n, d, e)
+    s = O.baseline_slopes(h)
+    got = run_lightning(q, k, v, do, s, torch.bfloat16)
+    ref = oracle_on_rounded(q, k, v, do, s, torch.bfloat16)
+    for t, r, key in zip(got, ref, ("o", "dq", "dk", "dv")):
+        assert O.max_rel_err(t, r) < TOL_BF16, key
+
+
+def test_tensor_wide_qk_is_sliced_bf16():
+    # d = 256: two 128-wide q/k slices, each on the tensor-core path, outputs summed
+    b, h, n, d, e = 1, 2, 512, 256, 128
+    q, k, v, do = O.make_inputs(92, b, h, n, d, e)
+    s = O.baseline_slopes(h)
+    got = run_lightning(q, k, v, do, s, torch.bfloat16)
+    r = [t.to(torch.bfloat16).float() for t in (q, k, v, do)]
+    ref = O.dense_closed_form(r[0], r[1], r[2], s, r[3])
+    for t, w, key in zip(got, ref, ("o", "dq", "dk", "dv")):
+        assert O.max_rel_err(t, w) < 2.5e-2, key     # o is a sum of two bf16-rounded slice outputs
+
+
+@pytest.mark.parametrize("d,e", [(64, 64), (64, 128), (128, 64)])
+def test_tensor_head64_variants(d, e):
+    """The 64-wide tensor-core instantiations are built but gated until they have been verified on a B200:
+    run with LASP_B200_TENSOR_HEAD64=1 (the library reads it once per process)."""
+    import os
+    if os.environ.get("LASP_B200_TENSOR_HEAD64") != "1":
+        pytest.skip("set LASP_B200_TENSOR_HEAD64=1 to exercise the gated 64-wide tensor-core kernels")
+    from lasp_b200 import engine
+    b, h, n = 2, 4, 512
+    assert engine.make_plan(b, h, n, d, e, torch.bfloat16).path_name == "tensor"
+    q, k, v, do = O.make_inputs(93 + d + e, b, h, n, d, e)
+    s = O.baseline_slopes(h)
+    got = run_lightning(q, k, v, do, s, torch.bfloat16)
+    ref = oracle_on_rounded(q, k, v, do, s, torch.bfloat16)
+    for t, r, key in zip(got, ref, ("o", "dq", "dk", "dv")):
+        assert O.max_rel_err(t, r) < TOL_BF16, (key, d, e)
+    assert engine.read_status() == 0
