@@ -39,6 +39,13 @@ extern "C" {
 
 #define LASP_B200_ABI_VERSION 1
 
+/* the library is built with hidden visibility; only the entry points below are exported */
+#if defined(__GNUC__)
+#define LASP_B200_API __attribute__((visibility("default")))
+#else
+#define LASP_B200_API
+#endif
+
 typedef enum {
   LASP_OK = 0,
   LASP_ERR_NULL = -1,       /* a required pointer is NULL */
@@ -103,55 +110,55 @@ typedef struct {
   size_t ws_bytes;
 } lasp_bwd_args;
 
-int lasp_b200_abi_version(void);
-const char* lasp_b200_strerror(int status);
+LASP_B200_API int lasp_b200_abi_version(void);
+LASP_B200_API const char* lasp_b200_strerror(int status);
 /* text of the last CUDA runtime error seen by this thread inside the library */
-const char* lasp_b200_last_cuda_error(void);
+LASP_B200_API const char* lasp_b200_last_cuda_error(void);
 
 /* Resolves LASP_PATH_AUTO; returns LASP_PATH_SIMT / LASP_PATH_TENSOR or a
  * negative status when the problem is invalid (lasp_forward's shape asserts,
  * lasp/lasp_fuse_parallel.py:1080-1085, made explicit). */
-int lasp_b200_resolve_path(const lasp_problem* p);
+LASP_B200_API int lasp_b200_resolve_path(const lasp_problem* p);
 /* tokens per chunk state for the resolved path */
-int lasp_b200_chunk_tokens(const lasp_problem* p);
-size_t lasp_b200_fwd_workspace_bytes(const lasp_problem* p);
-size_t lasp_b200_bwd_workspace_bytes(const lasp_problem* p);
+LASP_B200_API int lasp_b200_chunk_tokens(const lasp_problem* p);
+LASP_B200_API size_t lasp_b200_fwd_workspace_bytes(const lasp_problem* p);
+LASP_B200_API size_t lasp_b200_bwd_workspace_bytes(const lasp_problem* p);
 
 /* ---- forward phases -------------------------------------------------- */
 /* per-chunk local states sum_c lambda^(len-c) k_c v_c^T.
  * Replaces _fwd_kv_parallel, lasp/lasp_fuse_parallel.py:117-200. */
-int lasp_b200_fwd_chunk_states(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
+LASP_B200_API int lasp_b200_fwd_chunk_states(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
 /* exclusive decayed scan of the chunk states seeded with kv_in; writes kv_out.
  * Replaces _fwd_kv_reduce, lasp/lasp_fuse_parallel.py:203-257, and the host
  * update KV = block_decay*KV + kv, lasp/lasp_fuse_parallel.py:941-942. */
-int lasp_b200_fwd_scan(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
+LASP_B200_API int lasp_b200_fwd_scan(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
 /* O = intra-chunk masked product + decayed Q x prefix state.
  * Replaces _fwd_diag_kernel + _fwd_none_diag_kernel,
  * lasp/lasp_fuse_parallel.py:15-114,261-336 (== _fwd_kernel of
  * lasp/lightning_attention.py:6-83 and lasp/lasp_fuse.py:15-127). */
-int lasp_b200_fwd_output(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
+LASP_B200_API int lasp_b200_fwd_output(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
 /* the three phases back to back: lasp_forward, lasp/lasp_fuse.py:356-406 */
-int lasp_b200_forward(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
+LASP_B200_API int lasp_b200_forward(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
 
 /* ---- backward phases ------------------------------------------------- */
 /* per-chunk local dKV states sum_r lambda^r q_r do_r^T.
  * Replaces _bwd_dkv_parallel, lasp/lasp_fuse_parallel.py:522-604. */
-int lasp_b200_bwd_chunk_states(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
+LASP_B200_API int lasp_b200_bwd_chunk_states(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
 /* reverse exclusive decayed scan seeded with dkv_in; writes dkv_out.
  * Replaces _bwd_dkv_reduce, lasp/lasp_fuse_parallel.py:607-662, and the host
  * update DKV = block_decay*DKV + dkv, lasp/lasp_fuse_parallel.py:1067-1068. */
-int lasp_b200_bwd_scan(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
+LASP_B200_API int lasp_b200_bwd_scan(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
 /* dQ, dK, dV from the cached prefix states and the suffix dKV states.
  * Replaces _bwd_diag_kernel + _bwd_none_diag_kernel,
  * lasp/lasp_fuse_parallel.py:339-519,665-830 (== _bwd_intra_kernel +
  * _bwd_inter_kernel, lasp/lightning_attention.py:86-393). */
-int lasp_b200_bwd_grads(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
+LASP_B200_API int lasp_b200_bwd_grads(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
 /* the three phases back to back: lasp_backward, lasp/lasp_fuse.py:409-475 */
-int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
+LASP_B200_API int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
 
 /* x_out = exp(-s_h n) x_in + x_local on (b,h,d,e) fp32 states; x_in may be NULL.
  * Replaces the torch glue KV = block_decay*KV + kv, lasp/lasp_naive.py:565,614. */
-int lasp_b200_state_combine(int b, int h, int d, int e, int n, const float* s, const float* x_in,
+LASP_B200_API int lasp_b200_state_combine(int b, int h, int d, int e, int n, const float* s, const float* x_in,
                             const float* x_local, float* x_out, void* stream);
 
 /* ---- state relay over NVLink peer memory ------------------------------ */
@@ -160,7 +167,7 @@ int lasp_b200_state_combine(int b, int h, int d, int e, int n, const float* s, c
  * 0) or lasp_b200_bwd_chunk_states (reverse = 1).  Equals kv_out / dkv_out of
  * the scan phase with a zero incoming state, without touching the chunk states.
  * Replaces kv[:, :, -1] of lasp/lasp_fuse_parallel.py:941. */
-int lasp_b200_state_total(const lasp_problem* p, const void* ws, size_t ws_bytes, const float* s, float* total,
+LASP_B200_API int lasp_b200_state_total(const lasp_problem* p, const void* ws, size_t ws_bytes, const float* s, float* total,
                           int reverse, void* stream);
 
 /* The state exchange of a sequence-parallel group as ONE kernel over
@@ -200,13 +207,13 @@ typedef struct {
   uint32_t* peer_acks[8];    /* acknowledgement words of each position (entries < position are written) */
   int64_t wait_clocks;
 } lasp_exchange_args;
-int lasp_b200_state_exchange(const lasp_exchange_args* a, void* stream);
+LASP_B200_API int lasp_b200_state_exchange(const lasp_exchange_args* a, void* stream);
 
 /* Copies this device's sticky kernel-fault word to *status_host (synchronises
  * the stream) and clears it when clear != 0.  0 = no kernel reported a fault;
  * the tensor-core kernels set bits when one of their bounded waits (TMA
  * arrival, tcgen05 completion) runs out instead of spinning for ever. */
-int lasp_b200_read_status(int32_t* status_host, int clear, void* stream);
+LASP_B200_API int lasp_b200_read_status(int32_t* status_host, int clear, void* stream);
 
 /* Forward pass that allocates nothing and needs no workspace from the caller.
  * (No counterpart in the reference, whose launchers allocate with torch.)
@@ -230,7 +237,7 @@ int lasp_b200_read_status(int32_t* status_host, int clear, void* stream);
  *   - The prefix states are not kept for a backward pass: this is a
  *     forward-only (inference / prefill) entry point. */
 #define LASP_B200_STATIC_SCRATCH_BYTES (64u << 20)
-int lasp_b200_forward_static(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
+LASP_B200_API int lasp_b200_forward_static(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
 
 #ifdef __cplusplus
 }

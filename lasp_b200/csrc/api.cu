@@ -133,88 +133,123 @@ size_t lasp_b200_fwd_workspace_bytes(const lasp_problem* p) {
 
 size_t lasp_b200_bwd_workspace_bytes(const lasp_problem* p) { return lasp_b200_fwd_workspace_bytes(p); }
 
+}  // extern "C"
+
+namespace {
+
+// Programmatic dependent launch between the three kernels of a composite call (tensor path only).
+// Off unless LASP_B200_PDL=1 until it has been verified on a GPU.
+bool chain_launches() {
+  static const bool on = [] {
+    const char* v = getenv("LASP_B200_PDL");
+    return v && v[0] == '1';
+  }();
+  return on;
+}
+
+int fwd_chunk_states(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs, bool chained) {
+  if (m.path == LASP_PATH_TENSOR)
+    return cuda_fail(lasp::tensor_chunk_states(m, a->k, a->v, a->s, lasp::ws_local_bf16(a->ws), false, chained, cs));
+  return cuda_fail(lasp::simt_chunk_states(m, a->k, a->v, a->s, lasp::ws_states_f32(a->ws), false, cs));
+}
+
+int fwd_scan(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs, bool chained) {
+  if (m.path == LASP_PATH_TENSOR)
+    return cuda_fail(lasp::scan_states_bf16(m, a->s, lasp::ws_local_bf16(a->ws), lasp::ws_states_bf16(a->ws, m),
+                                            a->kv_in, a->kv_out, false, chained, cs));
+  return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_states_f32(a->ws), a->kv_in, a->kv_out, false, cs));
+}
+
+int fwd_output(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs, bool chained) {
+  if (m.path == LASP_PATH_TENSOR)
+    return cuda_fail(lasp::tensor_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_states_bf16(a->ws, m), a->o, chained,
+                                             cs));
+  return cuda_fail(lasp::simt_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_states_f32(a->ws), a->o, cs));
+}
+
+int bwd_chunk_states(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs, bool chained) {
+  if (m.path == LASP_PATH_TENSOR)
+    return cuda_fail(lasp::tensor_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_local_bf16(a->ws), true, chained, cs));
+  return cuda_fail(lasp::simt_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_states_f32(a->ws), true, cs));
+}
+
+int bwd_scan(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs, bool chained) {
+  if (m.path == LASP_PATH_TENSOR)
+    return cuda_fail(lasp::scan_states_bf16(m, a->s, lasp::ws_local_bf16(a->ws), lasp::ws_states_bf16(a->ws, m),
+                                            a->dkv_in, a->dkv_out, true, chained, cs));
+  return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_states_f32(a->ws), a->dkv_in, a->dkv_out, true, cs));
+}
+
+int bwd_grads(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs, bool chained) {
+  if (m.path == LASP_PATH_TENSOR)
+    return cuda_fail(lasp::tensor_bwd_grads(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_states_bf16(a->fwd_ws, m),
+                                            lasp::ws_states_bf16(a->ws, m), a->dq, a->dk, a->dv, chained, cs));
+  return cuda_fail(lasp::simt_bwd_grads(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_states_f32(a->fwd_ws),
+                                        lasp::ws_states_f32(a->ws), a->dq, a->dk, a->dv, cs));
+}
+
+}  // namespace
+
+extern "C" {
+
 // ---- forward --------------------------------------------------------------
 int lasp_b200_fwd_chunk_states(const lasp_problem* p, const lasp_fwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_fwd(p, a, &m, false);
-  if (st != LASP_OK) return st;
-  cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (m.path == LASP_PATH_TENSOR)
-    return cuda_fail(lasp::tensor_chunk_states(m, a->k, a->v, a->s, lasp::ws_local_bf16(a->ws), false, cs));
-  return cuda_fail(lasp::simt_chunk_states(m, a->k, a->v, a->s, lasp::ws_states_f32(a->ws), false, cs));
+  return st != LASP_OK ? st : fwd_chunk_states(m, a, static_cast<cudaStream_t>(stream), false);
 }
 
 int lasp_b200_fwd_scan(const lasp_problem* p, const lasp_fwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_fwd(p, a, &m, false);
-  if (st != LASP_OK) return st;
-  cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (m.path == LASP_PATH_TENSOR)
-    return cuda_fail(lasp::scan_states_bf16(m, a->s, lasp::ws_local_bf16(a->ws), lasp::ws_states_bf16(a->ws, m),
-                                            a->kv_in, a->kv_out, false, cs));
-  return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_states_f32(a->ws), a->kv_in, a->kv_out, false, cs));
+  return st != LASP_OK ? st : fwd_scan(m, a, static_cast<cudaStream_t>(stream), false);
 }
 
 int lasp_b200_fwd_output(const lasp_problem* p, const lasp_fwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_fwd(p, a, &m, true);
-  if (st != LASP_OK) return st;
-  cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (m.path == LASP_PATH_TENSOR)
-    return cuda_fail(lasp::tensor_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_states_bf16(a->ws, m), a->o, cs));
-  return cuda_fail(lasp::simt_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_states_f32(a->ws), a->o, cs));
+  return st != LASP_OK ? st : fwd_output(m, a, static_cast<cudaStream_t>(stream), false);
 }
 
 int lasp_b200_forward(const lasp_problem* p, const lasp_fwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_fwd(p, a, &m, true);
   if (st != LASP_OK) return st;
-  if ((st = lasp_b200_fwd_chunk_states(p, a, stream)) != LASP_OK) return st;
-  if ((st = lasp_b200_fwd_scan(p, a, stream)) != LASP_OK) return st;
-  return lasp_b200_fwd_output(p, a, stream);
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  const bool chained = chain_launches() && m.path == LASP_PATH_TENSOR;
+  if ((st = fwd_chunk_states(m, a, cs, chained)) != LASP_OK) return st;
+  if ((st = fwd_scan(m, a, cs, chained)) != LASP_OK) return st;
+  return fwd_output(m, a, cs, chained);
 }
 
 // ---- backward -------------------------------------------------------------
 int lasp_b200_bwd_chunk_states(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_bwd(p, a, &m, false);
-  if (st != LASP_OK) return st;
-  cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (m.path == LASP_PATH_TENSOR)
-    return cuda_fail(lasp::tensor_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_local_bf16(a->ws), true, cs));
-  return cuda_fail(lasp::simt_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_states_f32(a->ws), true, cs));
+  return st != LASP_OK ? st : bwd_chunk_states(m, a, static_cast<cudaStream_t>(stream), false);
 }
 
 int lasp_b200_bwd_scan(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_bwd(p, a, &m, false);
-  if (st != LASP_OK) return st;
-  cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (m.path == LASP_PATH_TENSOR)
-    return cuda_fail(lasp::scan_states_bf16(m, a->s, lasp::ws_local_bf16(a->ws), lasp::ws_states_bf16(a->ws, m),
-                                            a->dkv_in, a->dkv_out, true, cs));
-  return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_states_f32(a->ws), a->dkv_in, a->dkv_out, true, cs));
+  return st != LASP_OK ? st : bwd_scan(m, a, static_cast<cudaStream_t>(stream), false);
 }
 
 int lasp_b200_bwd_grads(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_bwd(p, a, &m, true);
-  if (st != LASP_OK) return st;
-  cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (m.path == LASP_PATH_TENSOR)
-    return cuda_fail(lasp::tensor_bwd_grads(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_states_bf16(a->fwd_ws, m),
-                                            lasp::ws_states_bf16(a->ws, m), a->dq, a->dk, a->dv, cs));
-  return cuda_fail(lasp::simt_bwd_grads(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_states_f32(a->fwd_ws),
-                                        lasp::ws_states_f32(a->ws), a->dq, a->dk, a->dv, cs));
+  return st != LASP_OK ? st : bwd_grads(m, a, static_cast<cudaStream_t>(stream), false);
 }
 
 int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_bwd(p, a, &m, true);
   if (st != LASP_OK) return st;
-  if ((st = lasp_b200_bwd_chunk_states(p, a, stream)) != LASP_OK) return st;
-  if ((st = lasp_b200_bwd_scan(p, a, stream)) != LASP_OK) return st;
-  return lasp_b200_bwd_grads(p, a, stream);
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  const bool chained = chain_launches() && m.path == LASP_PATH_TENSOR;
+  if ((st = bwd_chunk_states(m, a, cs, chained)) != LASP_OK) return st;
+  if ((st = bwd_scan(m, a, cs, chained)) != LASP_OK) return st;
+  return bwd_grads(m, a, cs, chained);
 }
 
 int lasp_b200_state_combine(int b, int h, int d, int e, int n, const float* s, const float* x_in,

@@ -63,7 +63,7 @@ cudaError_t simt_chunk_states(const Dims& m, const void* a, const void* bten, co
 cudaError_t scan_states(const Dims& m, const float* s, float* states, const float* x_in, float* x_out, bool reverse,
                         cudaStream_t st);
 cudaError_t scan_states_bf16(const Dims& m, const float* s, const __nv_bfloat16* local, __nv_bfloat16* prefix,
-                             const float* x_in, float* x_out, bool reverse, cudaStream_t st);
+                             const float* x_in, float* x_out, bool reverse, bool chained, cudaStream_t st);
 cudaError_t simt_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
                             const float* prefix, void* o, cudaStream_t st);
 cudaError_t simt_bwd_grads(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
@@ -78,13 +78,15 @@ cudaError_t state_total(const Dims& m, const float* s, const void* local, float*
 cudaError_t state_exchange(const lasp_exchange_args& a, cudaStream_t st);
 
 // tcgen05 path (tensor_kernels.cu)
+// chained = the launch is one of the three of a composite forward / backward call: the kernels then use
+// programmatic dependent launch so that each starts while the one ahead drains
 cudaError_t tensor_chunk_states(const Dims& m, const void* a, const void* bten, const float* s,
-                                __nv_bfloat16* states, bool backward, cudaStream_t st);
+                                __nv_bfloat16* states, bool backward, bool chained, cudaStream_t st);
 cudaError_t tensor_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
-                              const __nv_bfloat16* prefix, void* o, cudaStream_t st);
+                              const __nv_bfloat16* prefix, void* o, bool chained, cudaStream_t st);
 cudaError_t tensor_bwd_grads(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
                              const float* s, const __nv_bfloat16* prefix, const __nv_bfloat16* suffix, void* dq,
-                             void* dk, void* dv, cudaStream_t st);
+                             void* dk, void* dv, bool chained, cudaStream_t st);
 bool tensor_path_supported(const Dims& m);
 
 }  // namespace lasp

@@ -95,11 +95,17 @@ __global__ void __launch_bounds__(NT) k_chunk_states(const T* __restrict__ A, co
 // ---------------------------------------------------------------------------
 constexpr int kScanBatch = 8;
 
+template <bool PDL>
 __global__ void __launch_bounds__(256) k_scan_bf16(const float* __restrict__ s,
                                                    const __nv_bfloat16* __restrict__ local,
                                                    __nv_bfloat16* __restrict__ prefix,
                                                    const float* __restrict__ x_in, float* __restrict__ x_out, int h,
                                                    int n, int de, int nc, int chunk, int reverse) {
+  if constexpr (PDL) {
+    // programmatic dependent launch: everything this kernel reads is written by the kernel ahead
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
   const int bh = blockIdx.y;
   const int el = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (el >= de) return;
@@ -478,10 +484,25 @@ cudaError_t scan_states(const Dims& m, const float* s, float* states, const floa
 }
 
 cudaError_t scan_states_bf16(const Dims& m, const float* s, const __nv_bfloat16* local, __nv_bfloat16* prefix,
-                             const float* x_in, float* x_out, bool reverse, cudaStream_t st) {
+                             const float* x_in, float* x_out, bool reverse, bool chained, cudaStream_t st) {
   const int de = m.d * m.e;
   dim3 grid((de / 4 + 127) / 128, m.b * m.h);
-  k_scan_bf16<<<grid, 128, 0, st>>>(s, local, prefix, x_in, x_out, m.h, m.n, de, m.nc, m.chunk, reverse ? 1 : 0);
+  if (chained) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(128);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, k_scan_bf16<true>, s, local, prefix, x_in, x_out, m.h, m.n, de, m.nc,
+                                         m.chunk, reverse ? 1 : 0);
+    return err != cudaSuccess ? err : cudaGetLastError();
+  }
+  k_scan_bf16<false><<<grid, 128, 0, st>>>(s, local, prefix, x_in, x_out, m.h, m.n, de, m.nc, m.chunk,
+                                           reverse ? 1 : 0);
   return cudaGetLastError();
 }
 

@@ -131,7 +131,7 @@ __device__ __forceinline__ void stage_row32(uint32_t taddr1, uint32_t taddr2, fl
 // ---------------------------------------------------------------------------
 // chunk states: out[i][j] = sum_c w_c A[c][i] B[c][j]   (A = K or Q, B = V or dO)
 // ---------------------------------------------------------------------------
-template <int D, int E>
+template <int D, int E, bool PDL>
 __global__ void __launch_bounds__(128) k_tc_chunk_states(const __grid_constant__ CUtensorMap map_a,
                                                          const __grid_constant__ CUtensorMap map_b,
                                                          const float* __restrict__ s,
@@ -159,6 +159,11 @@ __global__ void __launch_bounds__(128) k_tc_chunk_states(const __grid_constant__
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  if constexpr (PDL) {
+    // inputs may come from the kernel ahead and the states may still be read by it
+    grid_dependency_wait();
+    if (tid == 0) grid_launch_dependents();
+  }
   const uint32_t tmem = tmem_slot;
   const int row0 = bh * n + chunk * C;
   if (tid == 0) {
@@ -255,7 +260,7 @@ __device__ __forceinline__ void masked_store32(uint32_t taddr, uint8_t* tile, in
 
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int D, int E>
+template <int D, int E, bool PDL>
 __global__ void __launch_bounds__(320, 1) k_tc_fwd_output(const __grid_constant__ CUtensorMap map_q,
                                                           const __grid_constant__ CUtensorMap map_k,
                                                           const __grid_constant__ CUtensorMap map_v,
@@ -271,13 +276,14 @@ __global__ void __launch_bounds__(320, 1) k_tc_fwd_output(const __grid_constant_
   uint8_t* sk[2] = {sp + kP, sp + kP + kK};
   uint8_t* sv[2] = {sp + kP + 2 * kK, sp + kP + 2 * kK + kV};
   uint8_t* so = sv[1] + kV;  // C x E staging tile of the output
-  __shared__ uint64_t qp_full, k_full[2], v_full[2], s_full[2], sm_ready[2], o_full[2], t_free[2];
+  __shared__ uint64_t qp_full, p_full, k_full[2], v_full[2], s_full[2], sm_ready[2], o_full[2], t_free[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int dead;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     dead = 0;
     mbar_init(&qp_full, 1);
+    mbar_init(&p_full, 1);   // used by the dependent-launch variant only: P arrives apart from Q
     for (int p = 0; p < 2; ++p) {
       mbar_init(&k_full[p], 1);
       mbar_init(&v_full[p], 1);
@@ -305,9 +311,22 @@ __global__ void __launch_bounds__(320, 1) k_tc_fwd_output(const __grid_constant_
         mbar_expect_tx(&v_full[p], kV);
         tma_load_3d(sv[p], &map_v, &v_full[p], 0, row0, 0);
         if (i >= 1) wait_or_fault(&s_full[(i - 1) & 1], ((i - 1) >> 1) & 1, &dead, kFaultMmaWait);  // Q, P read
-        mbar_expect_tx(&qp_full, kQ + kP);
-        tma_load_3d(sq, &map_q, &qp_full, 0, row0, 0);
-        tma_load_3d(sp, &map_p, &qp_full, 0, (bh * nc + chunk) * D, 0);
+        if constexpr (!PDL) {
+          mbar_expect_tx(&qp_full, kQ + kP);
+          tma_load_3d(sq, &map_q, &qp_full, 0, row0, 0);
+          tma_load_3d(sp, &map_p, &qp_full, 0, (bh * nc + chunk) * D, 0);
+        } else {
+          // q, k, v are older than the chain of launches this kernel belongs to and may be read at once;
+          // the prefix states are written by the scan just ahead: wait for it before the first P load
+          mbar_expect_tx(&qp_full, kQ);
+          tma_load_3d(sq, &map_q, &qp_full, 0, row0, 0);
+          if (i == 0) {
+            grid_dependency_wait();
+            grid_launch_dependents();
+          }
+          mbar_expect_tx(&p_full, kP);
+          tma_load_3d(sp, &map_p, &p_full, 0, (bh * nc + chunk) * D, 0);
+        }
       }
     }
   } else if (warp == 1) {
@@ -321,6 +340,10 @@ __global__ void __launch_bounds__(320, 1) k_tc_fwd_output(const __grid_constant_
         wait_or_fault(&k_full[p], ph2, &dead, kFaultTmaWait);
         tc_fence_after_sync();
         umma_gemm(t_s, Operand{smem_u32(sq), C, false}, Operand{smem_u32(sk[p]), C, false}, C, D / 16, false);
+        if constexpr (PDL) {
+          wait_or_fault(&p_full, i & 1, &dead, kFaultTmaWait);
+          tc_fence_after_sync();
+        }
         umma_gemm(t_o2, Operand{smem_u32(sq), C, false}, Operand{smem_u32(sp), D, true}, E, D / 16, false);
         umma_commit(&s_full[p]);
         wait_or_fault(&sm_ready[p], ph2, &dead, kFaultMmaWait);
@@ -354,7 +377,12 @@ __global__ void __launch_bounds__(320, 1) k_tc_fwd_output(const __grid_constant_
       wait_or_fault(&o_full[p], ph2, &dead, kFaultMmaWait);
       tc_fence_after_sync();
       // the staging tile is free once the previous tile's store has read it
-      if (cw == 0 && lane == 0) bulk_wait_read<0>();
+      if (cw == 0 && lane == 0) {
+        bulk_wait_read<0>();
+        if constexpr (PDL) {
+          if (i == 0) grid_dependency_wait();   // the output may still be read by a kernel ahead
+        }
+      }
       named_sync(1, 256);
       const float qd = decay_pow(sl2, row);
 #pragma unroll
@@ -397,7 +425,7 @@ __global__ void __launch_bounds__(320, 1) k_tc_fwd_output(const __grid_constant_
 //                      dK = T3, dV = T0 + lambda^(C-c) T1, staged one after the
 //                      other through the dS_m tile and stored by TMA
 // ---------------------------------------------------------------------------
-template <int D, int E>
+template <int D, int E, bool PDL>
 __global__ void __launch_bounds__(320, 1) k_tc_bwd_grads(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -445,6 +473,14 @@ __global__ void __launch_bounds__(320, 1) k_tc_bwd_grads(
         tma_load_3d(sk, &map_k, &bar_in, 0, row0, 0);
         tma_load_3d(sdo, &map_do, &bar_in, 0, row0, 0);
         tma_load_3d(sv, &map_v, &bar_in, 0, row0, 0);
+        if constexpr (PDL) {
+          // q, k, v, do are older than the chain of launches this kernel belongs to; the suffix states are
+          // written by the scan just ahead: wait for it before the first state load
+          if (i == 0) {
+            grid_dependency_wait();
+            grid_launch_dependents();
+          }
+        }
         mbar_expect_tx(&bar_st, 2 * D * E * 2);
         tma_load_3d(sp, &map_p, &bar_st, 0, (bh * nc + chunk) * D, 0);
         tma_load_3d(sdn, &map_dn, &bar_st, 0, (bh * nc + chunk) * D, 0);
@@ -512,6 +548,9 @@ __global__ void __launch_bounds__(320, 1) k_tc_bwd_grads(
       wait_or_fault(&b_done, ph, &dead, kFaultMmaWait);
       tc_fence_after_sync();
       // epilogue: three output tiles, one after the other through the staging tile
+      if constexpr (PDL) {
+        if (leader && i == 0) grid_dependency_wait();   // the outputs may still be read by a kernel ahead
+      }
 #pragma unroll
       for (int which = 0; which < 3; ++which) {
         if (which > 0) {
@@ -557,6 +596,23 @@ int sm_count() {
   return cached[dev];
 }
 
+// Launch with or without the programmatic-stream-serialization attribute (see grid_dependency_wait in sm100.cuh).
+template <typename... KArgs, typename... Args>
+cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool chained,
+                   Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chained ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename F>
 cudaError_t opt_in_smem(F* fn, size_t bytes) {
   cudaError_t err = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -588,22 +644,31 @@ struct Maps {
 
 template <int D, int E>
 cudaError_t launch_chunk_states(const Dims& m, const void* a, const void* bten, const float* s,
-                                __nv_bfloat16* states, bool backward, cudaStream_t st) {
+                                __nv_bfloat16* states, bool backward, bool chained, cudaStream_t st) {
   CUtensorMap ma, mb;
   const uint64_t rows = (uint64_t)m.b * m.h * m.n;
   cudaError_t err = tile_map(&ma, a, rows, D, C, "tensor map (chunk-state A)");
   if (err != cudaSuccess) return err;
   if ((err = tile_map(&mb, bten, rows, E, C, "tensor map (chunk-state B)")) != cudaSuccess) return err;
   const size_t smem = (size_t)C * (D + E) * 2 + 1024;
-  if ((err = opt_in_smem(k_tc_chunk_states<D, E>, smem)) != cudaSuccess) return err;
   dim3 grid(m.nc, m.b * m.h);
-  k_tc_chunk_states<D, E><<<grid, 128, smem, st>>>(ma, mb, s, states, m.h, m.n, m.nc, backward ? 1 : 0);
+  if (chained) {
+    if ((err = opt_in_smem(k_tc_chunk_states<D, E, true>, smem)) != cudaSuccess) return err;
+    if ((err = launch(k_tc_chunk_states<D, E, true>, grid, dim3(128), smem, st, true, ma, mb, s, states, m.h, m.n, m.nc,
+                      backward ? 1 : 0)) != cudaSuccess) {
+      g_failed_step = "launch of the chunk-state kernel";
+      return err;
+    }
+    return launched("launch of the chunk-state kernel");
+  }
+  if ((err = opt_in_smem(k_tc_chunk_states<D, E, false>, smem)) != cudaSuccess) return err;
+  k_tc_chunk_states<D, E, false><<<grid, 128, smem, st>>>(ma, mb, s, states, m.h, m.n, m.nc, backward ? 1 : 0);
   return cudaGetLastError();
 }
 
 template <int D, int E>
 cudaError_t launch_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
-                              const __nv_bfloat16* prefix, void* o, cudaStream_t st) {
+                              const __nv_bfloat16* prefix, void* o, bool chained, cudaStream_t st) {
   CUtensorMap mq, mk, mv, mp;
   const uint64_t rows = (uint64_t)m.b * m.h * m.n;
   cudaError_t err;
@@ -614,17 +679,26 @@ cudaError_t launch_fwd_output(const Dims& m, const void* q, const void* k, const
   CUtensorMap mo;
   if ((err = tile_map(&mo, o, rows, E, C, "tensor map (o)")) != cudaSuccess) return err;
   const size_t smem = (size_t)(C * D + D * E + 2 * C * C + 3 * C * E) * 2 + 1024;
-  if ((err = opt_in_smem(k_tc_fwd_output<D, E>, smem)) != cudaSuccess) return err;
   const int tiles = m.nc * m.b * m.h;
   const int ctas = tiles < sm_count() ? tiles : sm_count();
-  k_tc_fwd_output<D, E><<<ctas, 320, smem, st>>>(mq, mk, mv, mp, mo, s, m.h, m.n, m.nc, tiles);
+  if (chained) {
+    if ((err = opt_in_smem(k_tc_fwd_output<D, E, true>, smem)) != cudaSuccess) return err;
+    if ((err = launch(k_tc_fwd_output<D, E, true>, dim3(ctas), dim3(320), smem, st, true, mq, mk, mv, mp, mo, s, m.h, m.n,
+                      m.nc, tiles)) != cudaSuccess) {
+      g_failed_step = "launch of the forward output kernel";
+      return err;
+    }
+    return launched("launch of the forward output kernel");
+  }
+  if ((err = opt_in_smem(k_tc_fwd_output<D, E, false>, smem)) != cudaSuccess) return err;
+  k_tc_fwd_output<D, E, false><<<ctas, 320, smem, st>>>(mq, mk, mv, mp, mo, s, m.h, m.n, m.nc, tiles);
   return launched("launch of the forward output kernel");
 }
 
 template <int D, int E>
 cudaError_t launch_bwd_grads(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
                              const float* s, const __nv_bfloat16* prefix, const __nv_bfloat16* suffix, void* dq,
-                             void* dk, void* dv, cudaStream_t st) {
+                             void* dk, void* dv, bool chained, cudaStream_t st) {
   CUtensorMap mq, mk, mv, mdo, mp, mdn;
   const uint64_t rows = (uint64_t)m.b * m.h * m.n;
   const uint64_t srows = (uint64_t)m.b * m.h * m.nc * D;
@@ -642,10 +716,19 @@ cudaError_t launch_bwd_grads(const Dims& m, const void* q, const void* k, const 
   // Q, K, V, dO, Dn, dS_m, and the larger of P / S_m
   const size_t last = (size_t)(D * E > C * C ? D * E : C * C) * 2;
   const size_t smem = (size_t)(2 * C * D + 2 * C * E + D * E + C * C) * 2 + last + 1024;
-  if ((err = opt_in_smem(k_tc_bwd_grads<D, E>, smem)) != cudaSuccess) return err;
   const int tiles = m.nc * m.b * m.h;
   const int ctas = tiles < sm_count() ? tiles : sm_count();
-  k_tc_bwd_grads<D, E><<<ctas, 320, smem, st>>>(mq, mk, mv, mdo, mp, mdn, mdq, mdk, mdv, s, m.h, m.n, m.nc, tiles);
+  if (chained) {
+    if ((err = opt_in_smem(k_tc_bwd_grads<D, E, true>, smem)) != cudaSuccess) return err;
+    if ((err = launch(k_tc_bwd_grads<D, E, true>, dim3(ctas), dim3(320), smem, st, true, mq, mk, mv, mdo, mp, mdn, mdq,
+                      mdk, mdv, s, m.h, m.n, m.nc, tiles)) != cudaSuccess) {
+      g_failed_step = "launch of the backward gradient kernel";
+      return err;
+    }
+    return launched("launch of the backward gradient kernel");
+  }
+  if ((err = opt_in_smem(k_tc_bwd_grads<D, E, false>, smem)) != cudaSuccess) return err;
+  k_tc_bwd_grads<D, E, false><<<ctas, 320, smem, st>>>(mq, mk, mv, mdo, mp, mdn, mdq, mdk, mdv, s, m.h, m.n, m.nc, tiles);
   return launched("launch of the backward gradient kernel");
 }
 
@@ -678,23 +761,23 @@ bool tensor_path_supported(const Dims& m) {
   } while (0)
 
 cudaError_t tensor_chunk_states(const Dims& m, const void* a, const void* bten, const float* s,
-                                __nv_bfloat16* states, bool backward, cudaStream_t st) {
-#define LASP_CALL(DD, EE) launch_chunk_states<DD, EE>(m, a, bten, s, states, backward, st)
+                                __nv_bfloat16* states, bool backward, bool chained, cudaStream_t st) {
+#define LASP_CALL(DD, EE) launch_chunk_states<DD, EE>(m, a, bten, s, states, backward, chained, st)
   LASP_DISPATCH_DE(m, LASP_CALL);
 #undef LASP_CALL
 }
 
 cudaError_t tensor_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
-                              const __nv_bfloat16* prefix, void* o, cudaStream_t st) {
-#define LASP_CALL(DD, EE) launch_fwd_output<DD, EE>(m, q, k, v, s, prefix, o, st)
+                              const __nv_bfloat16* prefix, void* o, bool chained, cudaStream_t st) {
+#define LASP_CALL(DD, EE) launch_fwd_output<DD, EE>(m, q, k, v, s, prefix, o, chained, st)
   LASP_DISPATCH_DE(m, LASP_CALL);
 #undef LASP_CALL
 }
 
 cudaError_t tensor_bwd_grads(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
                              const float* s, const __nv_bfloat16* prefix, const __nv_bfloat16* suffix, void* dq,
-                             void* dk, void* dv, cudaStream_t st) {
-#define LASP_CALL(DD, EE) launch_bwd_grads<DD, EE>(m, q, k, v, d_o, s, prefix, suffix, dq, dk, dv, st)
+                             void* dk, void* dv, bool chained, cudaStream_t st) {
+#define LASP_CALL(DD, EE) launch_bwd_grads<DD, EE>(m, q, k, v, d_o, s, prefix, suffix, dq, dk, dv, chained, st)
   LASP_DISPATCH_DE(m, LASP_CALL);
 #undef LASP_CALL
 }
