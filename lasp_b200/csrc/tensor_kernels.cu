@@ -216,6 +216,143 @@ __global__ void __launch_bounds__(128) k_tc_chunk_states(const __grid_constant__
 }
 
 // ---------------------------------------------------------------------------
+// chunk states, persistent variant (selected with LASP_B200_CHUNK_STATES_V2=1 until verified on a GPU)
+//
+// Same arithmetic as k_tc_chunk_states.  One CTA per SM walks over tiles; ten warps in four roles:
+//   warp 0 (one lane)  producer: A and B tiles into a two-stage ring
+//   warp 1 (one lane)  tensor-core issuer, accumulators double buffered (2 x 128 columns)
+//   warps 2-5          scale the rows of A by their decay weights in place (row = thread)
+//   warps 6-9          accumulator -> bf16 -> swizzled staging tile -> one TMA store per tile
+// so the loads of tile i+1, the row scaling of tile i+1 and the store of tile i-1 overlap the MMA of tile i.
+// ---------------------------------------------------------------------------
+template <int D, int E>
+__global__ void __launch_bounds__(320, 1) k_tc_chunk_states_v2(const __grid_constant__ CUtensorMap map_a,
+                                                               const __grid_constant__ CUtensorMap map_b,
+                                                               const __grid_constant__ CUtensorMap map_out,
+                                                               const float* __restrict__ s, int h, int n, int nc,
+                                                               int num_tiles, int backward) {
+  constexpr int kA = C * D * 2, kB = C * E * 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  // per stage: A then B (with D = 64 the M = 128 MMA reads on from A into B, which is valid memory)
+  uint8_t* sa[2] = {smem, smem + kA + kB};
+  uint8_t* sb[2] = {smem + kA, smem + 2 * kA + kB};
+  uint8_t* so = smem + 2 * (kA + kB);   // D x E staging tile
+  __shared__ uint64_t full[2], scaled[2], mma_done[2], t_free[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int dead;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    dead = 0;
+    for (int j = 0; j < 2; ++j) {
+      mbar_init(&full[j], 1);
+      mbar_init(&scaled[j], 128);
+      mbar_init(&mma_done[j], 1);
+      mbar_init(&t_free[j], 128);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 2) tmem_alloc(&tmem_slot, 256);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int i = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++i) {
+        const int bh = t / nc, chunk = t - bh * nc, row0 = bh * n + chunk * C, j = i & 1;
+        if (i >= 2) wait_or_fault(&mma_done[j], ((i - 2) >> 1) & 1, &dead, kFaultMmaWait);  // stage j has been read
+        mbar_expect_tx(&full[j], kA + kB);
+        tma_load_3d(sa[j], &map_a, &full[j], 0, row0, 0);
+        tma_load_3d(sb[j], &map_b, &full[j], 0, row0, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int i = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++i) {
+        const int j = i & 1, ph = (i >> 1) & 1;
+        if (i >= 2) wait_or_fault(&t_free[j], ((i - 2) >> 1) & 1, &dead, kFaultMmaWait);  // accumulator j drained
+        wait_or_fault(&scaled[j], ph, &dead, kFaultTmaWait);
+        tc_fence_after_sync();
+        umma_gemm(tmem + 128 * j, Operand{smem_u32(sa[j]), C, true}, Operand{smem_u32(sb[j]), C, true}, E, C / 16,
+                  false);
+        umma_commit(&mma_done[j]);
+      }
+    }
+  } else if (warp < 6) {
+    const int row = tid - 64;   // 0..127: the token of the tile this thread scales
+    int i = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++i) {
+      const int bh = t / nc, j = i & 1, ph = (i >> 1) & 1;
+      const float sh = s[bh % h];
+      const float w = backward ? expf(-sh * (float)row) : expf(-sh * (float)(C - row));
+      wait_or_fault(&full[j], ph, &dead, kFaultTmaWait);
+#pragma unroll
+      for (int slab = 0; slab < D / 64; ++slab) {
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const int c16 = (jj + lane) & 7;  // spread the 16-byte chunks of a quarter warp over the banks
+          uint4* p = reinterpret_cast<uint4*>(sa[j] + slab * C * 128 + row * 128 + c16 * 16);
+          uint4 v = *p;
+          uint32_t* u = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u[q]));
+            u[q] = pack_bf16(f.x * w, f.y * w);
+          }
+          *p = v;
+        }
+      }
+      fence_async_smem();
+      mbar_arrive(&scaled[j]);
+    }
+  } else {
+    const int row = (warp & 3) * 32 + lane;   // tensor-memory lane = row of the state; warps 6..9 -> quarters 2,3,0,1
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const bool leader = (warp == 6 && lane == 0);
+    int i = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++i) {
+      const int j = i & 1, ph = (i >> 1) & 1;
+      wait_or_fault(&mma_done[j], ph, &dead, kFaultMmaWait);
+      tc_fence_after_sync();
+      if (leader) bulk_wait_read<0>();   // the previous tile's store has read the staging tile
+      named_sync(2, 128);
+      if (row < D) {
+#pragma unroll
+        for (int c0 = 0; c0 < E; c0 += 32) {
+          uint32_t a[32];
+          tmem_ld32(tmem + 128 * j + lane_base + c0, a);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 32; q += 8) {
+            const uint4 v = make_uint4(pack_bf16(__uint_as_float(a[q]), __uint_as_float(a[q + 1])),
+                                       pack_bf16(__uint_as_float(a[q + 2]), __uint_as_float(a[q + 3])),
+                                       pack_bf16(__uint_as_float(a[q + 4]), __uint_as_float(a[q + 5])),
+                                       pack_bf16(__uint_as_float(a[q + 6]), __uint_as_float(a[q + 7])));
+            *reinterpret_cast<uint4*>(so + tile_offset(row, c0 + q, D)) = v;
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&t_free[j]);
+      fence_async_smem();
+      named_sync(2, 128);
+      if (leader) {
+        tma_store_3d(&map_out, so, 0, t * D, 0);   // state tile t = (bh * nc + chunk)
+        bulk_commit();
+      }
+    }
+    if (leader) bulk_wait_all<0>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) tmem_dealloc(tmem, 256);
+}
+
+// ---------------------------------------------------------------------------
 // forward output: O = S_m V + diag(lambda^r) Q P      (persistent, pipelined)
 //
 // One CTA per SM walks over tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...
@@ -596,6 +733,14 @@ int sm_count() {
   return cached[dev];
 }
 
+bool chunk_states_v2_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("LASP_B200_CHUNK_STATES_V2");
+    return v && v[0] == '1';
+  }();
+  return on;
+}
+
 // Launch with or without the programmatic-stream-serialization attribute (see grid_dependency_wait in sm100.cuh).
 template <typename... KArgs, typename... Args>
 cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool chained,
@@ -651,6 +796,17 @@ cudaError_t launch_chunk_states(const Dims& m, const void* a, const void* bten, 
   if (err != cudaSuccess) return err;
   if ((err = tile_map(&mb, bten, rows, E, C, "tensor map (chunk-state B)")) != cudaSuccess) return err;
   const size_t smem = (size_t)C * (D + E) * 2 + 1024;
+  if (chunk_states_v2_enabled() && !chained) {
+    CUtensorMap mo;
+    if ((err = tile_map(&mo, states, (uint64_t)m.b * m.h * m.nc * D, E, D, "tensor map (chunk states)")) != cudaSuccess)
+      return err;
+    const size_t smem2 = (size_t)(2 * C * (D + E) + D * E) * 2 + 1024;
+    if ((err = opt_in_smem(k_tc_chunk_states_v2<D, E>, smem2)) != cudaSuccess) return err;
+    const int tiles = m.nc * m.b * m.h;
+    const int ctas = tiles < sm_count() ? tiles : sm_count();
+    k_tc_chunk_states_v2<D, E><<<ctas, 320, smem2, st>>>(ma, mb, mo, s, m.h, m.n, m.nc, tiles, backward ? 1 : 0);
+    return launched("launch of the persistent chunk-state kernel");
+  }
   dim3 grid(m.nc, m.b * m.h);
   if (chained) {
     if ((err = opt_in_smem(k_tc_chunk_states<D, E, true>, smem)) != cudaSuccess) return err;

@@ -325,3 +325,22 @@ def test_tensor_dependent_launch_variant():
         for t, r, key in zip(got, ref, ("o", "dq", "dk", "dv")):
             assert O.max_rel_err(t, r) < TOL_BF16, key
     assert engine.read_status() == 0
+
+
+def test_tensor_persistent_chunk_state_variant():
+    """The persistent chunk-state kernel is built but off by default until verified on a B200: run with
+    LASP_B200_CHUNK_STATES_V2=1 (read once per process).  Same arithmetic, so the same gates apply; the
+    outgoing states exercise the chunk states directly."""
+    import os
+    if os.environ.get("LASP_B200_CHUNK_STATES_V2") != "1":
+        pytest.skip("set LASP_B200_CHUNK_STATES_V2=1 to exercise the persistent chunk-state kernel")
+    from lasp_b200 import engine
+    for shape in [(1, 1, 128, 128, 128), (2, 12, 2048, 128, 128), (1, 3, 1024, 128, 128)]:
+        b, h, n, d, e = shape
+        q, k, v, do = O.make_inputs(96 + n, b, h, n, d, e)
+        s = O.baseline_slopes(h)
+        got = run_lightning(q, k, v, do, s, torch.bfloat16)
+        ref = oracle_on_rounded(q, k, v, do, s, torch.bfloat16)
+        for t, r, key in zip(got, ref, ("o", "dq", "dk", "dv")):
+            assert O.max_rel_err(t, r) < TOL_BF16, (key, shape)
+    assert engine.read_status() == 0
