@@ -88,3 +88,21 @@ def test_operators_refuse_cpu_tensors():
     q = torch.randn(1, 1, 64, 16)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         lightning_attn(q, q, q, torch.zeros(1, 1, 1))
+
+
+def test_exchange_argument_checks(lib):
+    a = _cabi.ExchangeArgs()
+    assert lib.lasp_b200_state_exchange(C.byref(a), None) == -1                      # NULL pointers
+    a.s, a.total, a.counters = 4096, 4096, 4096
+    a.b, a.h, a.d, a.e, a.n = 1, 1, 16, 16, 64
+    a.ranks, a.position = 9, 0
+    assert lib.lasp_b200_state_exchange(C.byref(a), None) == -2                      # more than 8 ranks
+    a.ranks, a.position = 4, 4
+    assert lib.lasp_b200_state_exchange(C.byref(a), None) == -2                      # position outside the group
+    a.ranks, a.position = 4, 1
+    assert lib.lasp_b200_state_exchange(C.byref(a), None) == -1                      # position > 0 needs x_in
+    a.x_in, a.my_slots = 4096, 4096
+    assert lib.lasp_b200_state_exchange(C.byref(a), None) == -1                      # missing ack / peer pointers
+    p = _problem()
+    assert lib.lasp_b200_state_total(C.byref(p), None, 0, None, None, 0, None) == -1
+    assert lib.lasp_b200_state_total(C.byref(p), 4096, 16, 4096, 4096, 0, None) == -5   # workspace too small
