@@ -1,11 +1,16 @@
 // Tensor-core path: tcgen05 MMAs with accumulators in tensor memory, operands
 // staged in shared memory by TMA.  bf16 inputs, fp32 accumulation, one rounding
-// on store.  One CTA owns one 128-token chunk of one (batch, head).
+// on store.  The unit of work is a tile: one 128-token chunk of one (batch, head).
 //
 // Every tile in shared memory is in the swizzled slab format of sm100.cuh, so a
 // tile loaded once serves both as a K-major operand (rows = M/N) and as an
 // MN-major operand (rows = K).  The decay mask is applied between MMAs on the
 // way from tensor memory back to shared memory (S -> S_m as bf16).
+//
+//   k_tc_chunk_states      one CTA per tile: (decay-scaled K)^T V or (decay-scaled Q)^T dO
+//   k_tc_chunk_states_v2   the same as a persistent pipeline (gated, see below)
+//   k_tc_fwd_output        persistent: O = S_m V + diag(lambda^r) Q P
+//   k_tc_bwd_grads         persistent: dQ, dK, dV
 //
 // All waits are bounded; a wait that runs out sets a bit in g_fault_word and the
 // CTA skips its remaining waits, frees its tensor memory and exits.
