@@ -306,8 +306,9 @@ def run_ours(args):
             with torch.cuda.stream(s_out):
                 s_out.wait_event(done)
                 for dst, src in zip(host_out, outs):
+                    src.record_stream(s_out)           # the allocator must not reuse it before the copy-out ran
                     dst.copy_(src, non_blocking=True)
-            keep[j] = outs                             # alive until the copy-out two steps later is long queued
+            keep[j] = outs
         cur.wait_stream(s_out)
         cur.wait_stream(s_in)
 
