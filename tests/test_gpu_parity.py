@@ -360,3 +360,36 @@ def test_no_decay_linear_transformer_config_bf16(width):
     gate = TOL_BF16 if width <= 128 else 2.5e-2          # 256: sums of bf16-rounded slice results
     for t, w, key in zip(got, ref, ("o", "dq", "dk", "dv")):
         assert O.max_rel_err(t, w) < gate, (key, width)
+
+
+def test_exchange_wait_runs_out_and_is_reported():
+    """Failure detection without a GPU fault: a gathering rank whose sender never writes.  The kernel's waits
+    are bounded, so it must come back on its own, set the relay bit (4) of the fault word, and leave the
+    context usable."""
+    import ctypes as C
+    from lasp_b200 import _cabi, engine
+    b, h, d, e, n = 1, 2, 32, 32, 64
+    elems = b * h * d * e
+    s = O.baseline_slopes(h).reshape(-1).to(DEV)
+    total = torch.randn(b, h, d, e, device=DEV)
+    x_in = torch.empty(b, h, d, e, device=DEV)
+    slots = torch.zeros(2 * 2 * elems * 2, dtype=torch.int32, device=DEV)      # {value, step} words, step 0 = stale
+    acks = torch.zeros(2 * 8 * 32, dtype=torch.int32, device=DEV)
+    counters = torch.zeros(64, dtype=torch.int32, device=DEV)
+    a = _cabi.ExchangeArgs()
+    a.b, a.h, a.d, a.e, a.n, a.ranks, a.position = b, h, d, e, n, 2, 1          # the last of two: gathers only
+    a.s, a.total, a.x_in = s.data_ptr(), total.data_ptr(), x_in.data_ptr()
+    a.my_slots, a.my_acks, a.counters = slots.data_ptr(), acks.data_ptr(), counters.data_ptr()
+    a.peer_acks[0] = acks.data_ptr()          # the absent sender's acknowledgement words: any writable memory
+    a.wait_clocks = 200000                    # about 0.1 ms
+    assert engine.read_status() == 0
+    _cabi.call("lasp_b200_state_exchange", C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert engine.read_status(clear=True) == 4
+    assert counters[0].item() == 1            # the step was still counted
+    # the device is fine: an ordinary call still works and reports no fault
+    q, k, v, do = O.make_inputs(98, 1, 2, 128, 32, 32)
+    got = run_lightning(q, k, v, do, O.baseline_slopes(2), torch.float32)
+    ref = O.fwd_bwd(q, k, v, O.baseline_slopes(2), do)
+    assert O.max_rel_err(got[0], ref[0]) < TOL_FP32
+    assert engine.read_status() == 0
