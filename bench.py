@@ -335,17 +335,28 @@ def run_ours(args):
         bw.grads()
     torch.cuda.synchronize()
     reps = 8 * n_sets
-    kg = torch.cuda.CUDAGraph()     # back-to-back launches of the one kernel, rotating over the input sets
-    with torch.cuda.graph(kg):
-        for i in range(reps):
-            bws[i % n_sets].grads()
-    kg.replay()
-    torch.cuda.synchronize()
-    start.record()
-    kg.replay()
-    stop.record()
-    torch.cuda.synchronize()
-    kernel_ms = start.elapsed_time(stop) / reps
+
+    def launch_ms(fn):
+        """average device time of one launch: a graph of back-to-back launches rotating over the input sets"""
+        kg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(kg):
+            for i in range(reps):
+                fn(i % n_sets)
+        kg.replay()
+        torch.cuda.synchronize()
+        start.record()
+        kg.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / reps
+
+    kernel_ms = launch_ms(lambda i: bws[i].grads())
+    phases = None
+    if args.phases:
+        phases = {name: 1e3 * launch_ms(fn) for name, fn in (
+            ("fwd_chunk_states_us", lambda i: fws[i].chunk_states()), ("fwd_scan_us", lambda i: fws[i].scan()),
+            ("fwd_output_us", lambda i: fws[i].output()), ("bwd_chunk_states_us", lambda i: bws[i].chunk_states()),
+            ("bwd_scan_us", lambda i: bws[i].scan()), ("bwd_grads_us", lambda i: bws[i].grads()))}
     kernel_bytes = (4 * D + 3 * E) * 2 * B * H * N_LOCAL      # reads q,k,v,do; writes dq,dk,dv
     achieved = kernel_bytes / (kernel_ms * 1e-3) / 1e9
     step_bytes = (6 * D + 5 * E) * 2 * B * H * N_LOCAL
@@ -388,6 +399,9 @@ def run_ours(args):
                          "sample": f"3 runs of one rank's chunk (b={B},h={H},n={N_LOCAL},d=e={D}) fp32, median"},
     }
     print(json.dumps(line), flush=True)
+    if phases is not None:
+        print(json.dumps({"phases": phases, "note": "device time per launch of each of the six kernels, L2-cold"}),
+              flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -401,6 +415,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dp", type=int, default=1, help="data-parallel size; sequence-parallel size = gpus / dp")
     ap.add_argument("--eager", action="store_true", help="time the public operator launch by launch (no CUDA graph)")
+    ap.add_argument("--phases", action="store_true", help="also print a second JSON line with the time of each kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
