@@ -231,6 +231,7 @@ def run_ours(args):
         step(i)
     sync_all()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    tokens_per_step = B * dp * N_LOCAL * sp
     with ClockSampler(local) as clocks:
         sync_all()
         start.record()
@@ -238,12 +239,30 @@ def run_ours(args):
             step(args.warmup + i)
         stop.record()
         sync_all()
-    ms = torch.tensor([start.elapsed_time(stop)], device=device)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_per_step = ms.item() / args.steps
-    tokens_per_step = B * dp * N_LOCAL * sp
+        ms = torch.tensor([start.elapsed_time(stop)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        ms_per_step = ms.item() / args.steps
+        # The timed region lasts a few milliseconds, too short for nvidia-smi to sample.  Keep the same
+        # steps running for about a second under the sampler: its clocks and throttle reasons are those of
+        # this load, and the longer window gives a sustained figure next to the timed one.
+        extra = int(min(20000, max(args.steps, 1000.0 / max(ms_per_step, 1e-3))))
+        t2 = torch.tensor([extra], device=device)
+        if world > 1:
+            dist.all_reduce(t2, op=dist.ReduceOp.MIN)
+        extra = int(t2.item())
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s2.record()
+        for i in range(extra):
+            step(i)
+        e2.record()
+        sync_all()
+        ms_sus = torch.tensor([s2.elapsed_time(e2)], device=device)
+        if world > 1:
+            dist.all_reduce(ms_sus, op=dist.ReduceOp.MAX)
     value = tokens_per_step / (ms_per_step * 1e-3)
+    sustained = {"value": tokens_per_step / (ms_sus.item() / extra * 1e-3), "unit": UNIT, "steps": extra,
+                 "ms_per_step": ms_sus.item() / extra}
 
     # ---- end to end through the public operator with host buffers ---------
     host_in = make_set(5000 + rank, device, dtype, pinned=True)
@@ -388,7 +407,7 @@ def run_ours(args):
                 "steps": e2e_steps, "mode": e2e_mode, "serial_value": e2e_serial},
         "gpu_launches": (graphs[0][1].launches if graphs else 6) * args.steps,
         "kernel_faults": fault_word,
-        "clocks": clocks.summary(),
+        "clocks": clocks.summary(), "sustained": sustained,
         "roofline": {"bound": "hbm", "kernel": f"bwd_grads ({plan.path_name})", "achieved": achieved,
                      "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_kind,
                      "traffic": DOMINANT_KERNEL_TRAFFIC_BYTES, "kernel_ms": kernel_ms,
