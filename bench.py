@@ -188,6 +188,7 @@ def run_ours(args):
 
     plan = engine.make_plan(B, H, N_LOCAL, D, E, dtype)
     graphs = []
+    graph_note = "eager operator calls"
     if not args.eager:
         # the launches of a step (6 kernels; 10 with the two state totals and the two
         # relay hops of a sequence-parallel rank) go through the C ABI and are replayed
@@ -196,8 +197,16 @@ def run_ours(args):
         from lasp_b200.utils import get_sequence_parallel_group
         group = get_sequence_parallel_group() if world > 1 else None
         side = torch.cuda.Stream()
-        for q, k, v, do in sets:
-            fixed = FixedStep(q.detach(), k.detach(), v.detach(), do, s, group)
+        try:
+            fixed_steps = [FixedStep(q.detach(), k.detach(), v.detach(), do, s, group) for q, k, v, do in sets]
+            usable = 1
+        except Exception as exc:  # noqa: BLE001  (no peer-mapped exchange here: time the eager NCCL path)
+            graph_note = f"eager operator calls ({type(exc).__name__}: {exc})"[:200]
+            fixed_steps, usable = [], 0
+        flag = torch.tensor([usable], device=device)
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)      # all ranks take the same route
+        for fixed in (fixed_steps if flag.item() else []):
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
                 fixed.run()
@@ -399,7 +408,7 @@ def run_ours(args):
                                "d=e=128, decay 2^(-8(i+1)/12)", "parallelism": f"dp{dp}xsp{sp}",
                    "global_batch": B * dp, "global_seq_len": N_LOCAL * sp, "kernel_path": plan.path_name,
                    "launch": f"cuda graph of the {graphs[0][1].launches} C-ABI launches" if graphs
-                   else "eager operator calls",
+                   else graph_note,
                    "transport": ("nvlink relay kernel" if graphs else "nccl or nvlink (operator default)")
                    if world > 1 else "none",
                    "l2": f"inputs rotate over {n_sets} independent sets ({n_sets * set_bytes / 1e6:.0f} MB) > L2"},
