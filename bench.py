@@ -191,7 +191,7 @@ def run_ours(args):
     graph_note = "eager operator calls"
     if not args.eager:
         # the launches of a step (6 kernels; 10 with the two state totals and the two
-        # relay hops of a sequence-parallel rank) go through the C ABI and are replayed
+        # state exchanges of a sequence-parallel rank) go through the C ABI and are replayed
         # from a CUDA graph, one graph per input set
         from lasp_b200.pipeline import FixedStep
         from lasp_b200.utils import get_sequence_parallel_group
@@ -409,7 +409,7 @@ def run_ours(args):
                    "global_batch": B * dp, "global_seq_len": N_LOCAL * sp, "kernel_path": plan.path_name,
                    "launch": f"cuda graph of the {graphs[0][1].launches} C-ABI launches" if graphs
                    else graph_note,
-                   "transport": ("nvlink relay kernel" if graphs else "nccl or nvlink (operator default)")
+                   "transport": ("nvlink exchange kernel" if graphs else "nccl or nvlink (operator default)")
                    if world > 1 else "none",
                    "l2": f"inputs rotate over {n_sets} independent sets ({n_sets * set_bytes / 1e6:.0f} MB) > L2"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
