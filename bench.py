@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload: BASELINE config 1 - per rank b=2, h=12, 2048 tokens, d=e=128, bf16,
+Workload (the headline configuration): per rank b=2, h=12, 2048 tokens, d=e=128, bf16,
 seeded synthetic N(0,1) inputs (q,k scaled by d^-0.5), slopes 2^(-8(i+1)/12).
 With N GPUs the N ranks form one sequence-parallel group (DP=1, SP=N; global
 sequence 2048*N) unless --dp says otherwise; per-rank work is fixed (weak
@@ -36,7 +36,7 @@ sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
-# BASELINE config 1, per rank
+# headline configuration, per rank
 B, H, N_LOCAL, D, E = 2, 12, 2048, 128, 128
 METRIC = "fwd+bwd tokens/s, LASP linear attention (b=2/rank, h=12, 2048 tokens/rank, d=e=128)"
 UNIT = "tokens/s"

@@ -128,7 +128,9 @@ def sp_worker(rank, world, port, ref_path, name, p, outdir):
 
 
 def main():
-    ref_path = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/LASP")
+    ref_path = sys.argv[1]
     lasp = import_reference(ref_path)
     meta = {"single": SINGLE_CASES, "sp": SP_CASES, "variants": VARIANTS}
     for name, p in SINGLE_CASES.items():

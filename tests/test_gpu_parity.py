@@ -210,7 +210,7 @@ TENSOR_SHAPES = [
     (1, 1, 128, 128, 128),     # a single tile
     (2, 3, 256, 128, 128),
     (1, 2, 1024, 128, 128),
-    (2, 12, 2048, 128, 128),   # BASELINE config 1, one rank
+    (2, 12, 2048, 128, 128),   # the headline configuration, one rank
 ]
 
 
@@ -348,7 +348,7 @@ def test_tensor_persistent_chunk_state_variant():
 
 @pytest.mark.parametrize("width", [64, 128, 256])
 def test_no_decay_linear_transformer_config_bf16(width):
-    """BASELINE config 4 at reduced length: s = 0, elu(x)+1 feature map on q and k (applied by the caller, no
+    """The no-decay (LinearTransformer-style) configuration at reduced length: s = 0, elu(x)+1 feature map on q and k (applied by the caller, no
     1/sqrt(d)), d = e in {64, 128, 256}, bf16.  64 runs on the fp32-accumulating FFMA kernels, 128 on the
     tensor-core kernels, 256 as 128-wide slices of both head dimensions."""
     b, h, n = 1, 2, 1024

@@ -145,7 +145,7 @@ def _sweep():
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
 def test_dp_sp_sweep_baseline_config1(dtype):
-    """BASELINE config 1: every DP x SP factorisation of the box; per rank b=2,
+    """The headline configuration: every DP x SP factorisation of the box; per rank b=2,
     2048 tokens, h=12, d=e=128 (bf16: tensor-core path; fp32: FFMA path)."""
     if _ngpu() < 2:
         pytest.skip("needs >= 2 GPUs")

@@ -1,4 +1,4 @@
-"""Error budget of the tensor-core path, checked on the CPU.
+"""Rounding-error model of the tensor-core path, checked on the CPU.
 
 The tensor-core kernels round to bf16 at fixed points: the decay-scaled K / Q rows of the chunk-state products,
 the per-chunk local states, the per-chunk prefix / suffix states (MMA operands), the masked S and dS matrices,
