@@ -43,8 +43,8 @@ UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
 L2_BYTES = 126e6
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (backward gradients) on this
-# workload, from the ncu capture summarised in profiles/bwd_grads_tensor_v1_cfg1.md: 75.7 MB read (q,k,v,do and the
-# two state tensors) + 5.6 MB written back by kernel end (most of dq,dk,dv still sits in L2)
+# workload, from one ncu capture: 75.7 MB read (q,k,v,do and the two state tensors) + 5.6 MB written back by
+# kernel end (most of dq,dk,dv still sits in L2)
 DOMINANT_KERNEL_TRAFFIC_BYTES = 81.3e6
 
 
