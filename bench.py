@@ -203,9 +203,22 @@ def run_ours(args):
         except Exception as exc:  # noqa: BLE001  (no peer-mapped exchange here: time the eager NCCL path)
             graph_note = f"eager operator calls ({type(exc).__name__}: {exc})"[:200]
             fixed_steps, usable = [], 0
+        if usable and world > 1:
+            # self-check of the exchange before anything is timed: one eager step; a bounded wait that ran out
+            # (fault word != 0 on any rank) sends every rank down the NCCL route instead
+            fixed_steps[0].run()
+            torch.cuda.synchronize()
+            if engine.read_status(clear=True) != 0:
+                usable = 0
+                graph_note = "eager operator calls over NCCL (the exchange self-check reported a fault)"
         flag = torch.tensor([usable], device=device)
         if world > 1:
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)      # all ranks take the same route
+        if world > 1 and not flag.item():
+            from lasp_b200 import comm
+            comm._relay_unavailable = True                   # the operators now use NCCL send/recv
+            if usable:
+                graph_note = "eager operator calls over NCCL (the exchange self-check failed on another rank)"
         for fixed in (fixed_steps if flag.item() else []):
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
