@@ -70,6 +70,25 @@ class _on_device:
         return False
 
 
+_NVTX = os.environ.get("LASP_B200_NVTX", "0") == "1"
+
+
+class _traced:
+    """NVTX range around a library call (LASP_B200_NVTX=1), for timeline tools."""
+
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        if _NVTX:
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if _NVTX:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 def _require_cuda(*ts):
     for t in ts:
         if t is not None and not t.is_cuda:
@@ -117,7 +136,7 @@ class Forward:
                                    _ptr(self.o), _ptr(self.ws), self.ws.numel())
 
     def _call(self, fn):
-        with _on_device(self.q.device):
+        with _on_device(self.q.device), _traced(fn):
             _cabi.call(fn, C.byref(self.plan.problem), C.byref(self._args), _stream())
 
     def chunk_states(self):
@@ -149,7 +168,7 @@ class Backward:
                                    _ptr(self.ws), self.ws.numel())
 
     def _call(self, fn):
-        with _on_device(self.keep[0].device):
+        with _on_device(self.keep[0].device), _traced(fn):
             _cabi.call(fn, C.byref(self.plan.problem), C.byref(self._args), _stream())
 
     def chunk_states(self):
@@ -190,7 +209,7 @@ def state_total(plan: Plan, ws: torch.Tensor, s, reverse: bool, out=None):
 
 
 def state_exchange(args: "_cabi.ExchangeArgs", device) -> None:
-    with _on_device(device):
+    with _on_device(device), _traced("lasp_b200_state_exchange"):
         _cabi.call("lasp_b200_state_exchange", C.byref(args), _stream())
 
 

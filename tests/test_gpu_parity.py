@@ -393,3 +393,41 @@ def test_exchange_wait_runs_out_and_is_reported():
     ref = O.fwd_bwd(q, k, v, O.baseline_slopes(2), do)
     assert O.max_rel_err(got[0], ref[0]) < TOL_FP32
     assert engine.read_status() == 0
+
+
+@pytest.mark.parametrize("path,dtype,shape", [("tensor", torch.bfloat16, (2, 3, 512, 128, 128)),
+                                              ("simt", torch.float32, (1, 2, 333, 64, 48))])
+def test_runs_are_bitwise_repeatable(path, dtype, shape, monkeypatch):
+    """No atomics or order-dependent reductions on the data path: two runs give identical bits."""
+    b, h, n, d, e = shape
+    q, k, v, do = O.make_inputs(99, b, h, n, d, e)
+    s = O.baseline_slopes(h)
+    first = run_lightning(q, k, v, do, s, dtype, path, monkeypatch)
+    second = run_lightning(q, k, v, do, s, dtype, path, monkeypatch)
+    for a, bb in zip(first, second):
+        assert torch.equal(a, bb)
+
+
+@pytest.mark.parametrize("path,dtype,shape", [("tensor", torch.bfloat16, (1, 2, 256, 128, 128)),
+                                              ("simt", torch.float32, (1, 2, 100, 32, 48))])
+def test_forward_writes_stay_inside_their_buffers(path, dtype, shape):
+    """Canaries around the output and the workspace: nothing is written outside what the caller handed over."""
+    from lasp_b200 import engine
+    b, h, n, d, e = shape
+    q, k, v, _ = O.make_inputs(100, b, h, n, d, e)
+    q, k, v = (t.to(DEV, dtype) for t in (q, k, v))
+    s = O.baseline_slopes(h).to(DEV)
+    plan = engine.make_plan(b, h, n, d, e, dtype, path)
+    pad = 4096
+    o_buf = torch.full((b * h * n * e + 2 * pad,), 7.0, dtype=dtype, device=DEV)
+    ws_buf = torch.full((plan.ws_bytes + 2 * pad,), 0x5A, dtype=torch.uint8, device=DEV)
+    o = o_buf[pad:pad + b * h * n * e].view(b, h, n, e)
+    ws = ws_buf[pad:pad + plan.ws_bytes]
+    kv_out = torch.empty(b, h, d, e, device=DEV)
+    engine.Forward(plan, q, k, v, s, kv_out=kv_out, o=o, ws=ws).run()
+    torch.cuda.synchronize()
+    assert torch.all(o_buf[:pad] == 7.0) and torch.all(o_buf[-pad:] == 7.0)
+    assert torch.all(ws_buf[:pad] == 0x5A) and torch.all(ws_buf[-pad:] == 0x5A)
+    ref, kv_ref = O.blocked_forward(q.float().cpu(), k.float().cpu(), v.float().cpu(), s.cpu())
+    assert O.max_rel_err(o, ref) < _tol(dtype)
+    assert O.max_rel_err(kv_out, kv_ref) < 1e-2
