@@ -103,3 +103,36 @@ def test_sequence_parallel_operators_on_gloo(name):
         while not errq.empty():
             msgs.append(errq.get())
         pytest.fail("\n".join(msgs) or "worker failed")
+
+
+def _dead_peer_worker(rank, world, port, resq):
+    import datetime
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    import lasp_b200._core as core
+    from tests import fake_engine
+    core.ENGINE = fake_engine
+    import lasp
+    from lasp.utils import initialize_lasp
+    initialize_lasp(1, 2)
+    q, k, v, _ = O.make_inputs(1, 1, 1, 128, 16, 16)
+    s = O.baseline_slopes(1)
+    if rank == 0:
+        resq.put((0, "left"))          # the first rank leaves between steps and never sends its state
+        return
+    try:
+        lasp.lasp_naive(q[:, :, 64:], k[:, :, 64:], v[:, :, 64:], s)
+        resq.put((1, "no error"))
+    except Exception as exc:  # noqa: BLE001
+        resq.put((1, type(exc).__name__))
+
+
+def test_missing_sender_is_reported_by_a_timeout_not_a_hang():
+    """Failure detection on the host: the rank that should send the KV state is gone; the receiver's
+    blocking receive ends with an error after the process-group timeout instead of waiting for ever."""
+    ctx = mp.get_context("spawn")
+    resq = ctx.SimpleQueue()
+    mp.spawn(_dead_peer_worker, args=(2, _free_port(), resq), nprocs=2, join=True)
+    got = dict(resq.get() for _ in range(2))
+    assert got[0] == "left"
+    assert got[1] != "no error", "the receive should have timed out"
