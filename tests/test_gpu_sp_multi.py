@@ -80,7 +80,7 @@ def _worker(rank, world, port, mode, params, errq):
                 g = torch.Generator().manual_seed(((p["seed"] * 4 + which) * 4096 + b_global) * 64 + chunk)
                 width = p["d"] if which < 2 else p["e"]
                 t = torch.randn(p["h"], nl, width, generator=g)
-                return t * p["d"] ** -0.5 if which < 2 else t
+                return t * p["d"] ** -0.5 if (which < 2 and p.get("scale_qk", True)) else t
 
             rows = [i * p["dp"] + dp_rank for i in range(bl)]   # batch interleaved over dp
             qi, ki, vi, doi = (torch.stack([piece(w, bg, sp_rank) for bg in rows]).to(dtype).to(dev)
@@ -153,4 +153,17 @@ def test_dp_sp_sweep_baseline_config1(dtype):
     for dp, sp in sweep:
         p = dict(seed=70 + dp, dp=dp, sp=sp, b=2 * dp, h=12, n=2048 * sp, d=128, e=128, slopes="baseline",
                  dtype=dtype, check_heads=[0, 6, 11])
+        _launch(dp * sp, "oracle", p)
+
+
+def test_reference_test_shape_on_the_whole_box():
+    """The shape of the reference's own smoke test (tests/test.py:95 there): global batch 2 per GPU, global
+    n = 2048 cut over the SP group, h = 12, d = 128, e = 64, unscaled N(0,1) q and k, build_slope_tensor(12),
+    bf16; every DP x SP factorisation of the box."""
+    if _ngpu() < 2:
+        pytest.skip("needs >= 2 GPUs")
+    world = _ngpu()
+    for dp, sp in _sweep():
+        p = dict(seed=90 + dp, dp=dp, sp=sp, b=2 * world, h=12, n=2048, d=128, e=64, slopes="alibi",
+                 dtype="bfloat16", check_heads=[0, 5, 11], scale_qk=False)
         _launch(dp * sp, "oracle", p)
