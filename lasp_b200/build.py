@@ -17,7 +17,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "liblasp_b200.so")
-SOURCES = ["api.cu", "simt_kernels.cu", "tensor_kernels.cu", "relay_kernels.cu", "static_scratch.cu"]
+SOURCES = ["api.cu", "simt_kernels.cu", "tensor_kernels.cu", "walk_kernels.cu", "relay_kernels.cu", "static_scratch.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -45,6 +45,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
                      "-I", CSRC]
     if verbose:
         common += ["-Xptxas", "-v"]
+    if os.environ.get("LASP_TRACE") == "1":
+        common += ["-DLASP_TRACE"]
     procs = []
     for src in SOURCES:
         path = os.path.join(CSRC, src)

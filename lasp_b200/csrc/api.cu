@@ -3,10 +3,30 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace lasp {
 thread_local const char* g_failed_step = "";
+
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!cached[dev]) {
+    int v = 0;
+    cached[dev] = (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) ? v : 148;
+  }
+  return cached[dev];
+}
+
+// The tensor-core path takes bf16 with head widths 64 or 128 and at least one full tile per sequence;
+// a ragged last tile is handled by the TMA bounds of the walk kernels.
+bool tensor_path_supported(const Dims& m) {
+  const bool dims_ok = (m.d == 64 || m.d == 128) && (m.e == 64 || m.e == 128);
+  return m.dtype == LASP_BF16 && dims_ok && m.n >= kTensorTile;
+}
 }
 
 namespace {
@@ -35,6 +55,30 @@ void bind_context_once() {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// LASP_B200_TENSOR_IMPL=tile selects the per-tile tensor-core kernels (one bf16 state per 128 tokens in
+// global memory) instead of the walk kernels; LASP_B200_SPAN_TILES=k fixes the span length.  Read once.
+bool tile_kernels_requested() {
+  static const bool on = [] {
+    const char* v = getenv("LASP_B200_TENSOR_IMPL");
+    return v && v[0] == 't';
+  }();
+  return on;
+}
+bool unfused_requested() {
+  static const bool on = [] {
+    const char* v = getenv("LASP_B200_UNFUSED");
+    return v && v[0] == '1';
+  }();
+  return on;
+}
+int span_tiles_requested() {
+  static const int k = [] {
+    const char* v = getenv("LASP_B200_SPAN_TILES");
+    return v ? atoi(v) : 0;
+  }();
+  return k;
+}
+
 // validates the problem and fills Dims; returns LASP_OK or a negative status
 int make_dims(const lasp_problem* p, lasp::Dims* m) {
   if (!p) return LASP_ERR_NULL;
@@ -45,23 +89,50 @@ int make_dims(const lasp_problem* p, lasp::Dims* m) {
   if ((long long)p->b * p->h > 65535) return LASP_ERR_SHAPE;
   m->b = p->b; m->h = p->h; m->n = p->n; m->d = p->d; m->e = p->e;
   m->dtype = p->dtype;
-  m->chunk = lasp::kTensorChunk;
-  m->nc = (p->n + m->chunk - 1) / m->chunk;
+  m->walk = 0;
+  m->tiles = (p->n + lasp::kTensorTile - 1) / lasp::kTensorTile;
+  m->span = 1;
   const bool tensor_ok = lasp::tensor_path_supported(*m);
   int path = p->path;
   if (path == LASP_PATH_AUTO) path = tensor_ok ? LASP_PATH_TENSOR : LASP_PATH_SIMT;
   if (path == LASP_PATH_TENSOR && !tensor_ok) return LASP_ERR_PATH;
   if (path != LASP_PATH_TENSOR && path != LASP_PATH_SIMT) return LASP_ERR_PATH;
   m->path = path;
-  m->chunk = (path == LASP_PATH_TENSOR) ? lasp::kTensorChunk : lasp::kSimtChunk;
-  m->nc = (p->n + m->chunk - 1) / m->chunk;
+  if (path == LASP_PATH_SIMT) {
+    m->chunk = lasp::kSimtChunk;
+    m->nc = (p->n + m->chunk - 1) / m->chunk;
+    return LASP_OK;
+  }
+  if (tile_kernels_requested() && lasp::tensor_tile_path_supported(*m)) {
+    m->chunk = lasp::kTensorTile;
+    m->nc = m->tiles;
+    return LASP_OK;
+  }
+  // Spans: as few tiles per span as keeps the number of spans (= work items of the persistent kernels,
+  // b*h per span index) within one CTA per SM; a sequence-rich problem gets one span per sequence.
+  m->walk = 1;
+  int span = span_tiles_requested();
+  if (span <= 0) {
+    const int per_seq = lasp::sm_count() / (p->b * p->h);
+    span = per_seq >= 1 ? (m->tiles + per_seq - 1) / per_seq : m->tiles;
+  }
+  if (span > m->tiles) span = m->tiles;
+  m->span = span;
+  m->chunk = span * lasp::kTensorTile;
+  m->nc = (m->tiles + span - 1) / span;
   return LASP_OK;
 }
 
 size_t workspace_bytes(const lasp::Dims& m) {
   size_t s = lasp::state_elems(m);
-  size_t bytes = s * 4;  // fp32 states (SIMT) or bf16 local + bf16 prefix states (TENSOR)
+  size_t bytes = s * 4;  // fp32 states (SIMT) or bf16 local + bf16 prefix states (TENSOR, per tile)
+  if (m.walk) bytes = lasp::kWalkSyncBytes + 2 * s * 4;
   return (bytes + 255) & ~(size_t)255;
+}
+
+// one launch per direction when the CTAs of a launch can all be resident (or do not depend on each other)
+bool fusable(const lasp::Dims& m) {
+  return m.walk && !unfused_requested() && (m.nc == 1 || m.b * m.h * m.nc <= lasp::sm_count());
 }
 
 int check_fwd(const lasp_problem* p, const lasp_fwd_args* a, lasp::Dims* m, bool need_qo) {
@@ -148,19 +219,23 @@ bool chain_launches() {
 }
 
 int fwd_chunk_states(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs, bool chained) {
+  if (m.walk) return cuda_fail(lasp::walk_span_totals(m, a->k, a->v, a->s, lasp::ws_walk_border(a->ws, m), false, cs));
   if (m.path == LASP_PATH_TENSOR)
     return cuda_fail(lasp::tensor_chunk_states(m, a->k, a->v, a->s, lasp::ws_local_bf16(a->ws), false, chained, cs));
   return cuda_fail(lasp::simt_chunk_states(m, a->k, a->v, a->s, lasp::ws_states_f32(a->ws), false, cs));
 }
 
 int fwd_scan(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs, bool chained) {
-  if (m.path == LASP_PATH_TENSOR)
+  if (m.path == LASP_PATH_TENSOR && !m.walk)
     return cuda_fail(lasp::scan_states_bf16(m, a->s, lasp::ws_local_bf16(a->ws), lasp::ws_states_bf16(a->ws, m),
                                             a->kv_in, a->kv_out, false, chained, cs));
-  return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_states_f32(a->ws), a->kv_in, a->kv_out, false, cs));
+  float* states = m.walk ? lasp::ws_walk_border(a->ws, m) : lasp::ws_states_f32(a->ws);
+  return cuda_fail(lasp::scan_states(m, a->s, states, a->kv_in, a->kv_out, false, cs));
 }
 
 int fwd_output(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs, bool chained) {
+  if (m.walk)
+    return cuda_fail(lasp::walk_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_walk_border(a->ws, m), a->o, cs));
   if (m.path == LASP_PATH_TENSOR)
     return cuda_fail(lasp::tensor_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_states_bf16(a->ws, m), a->o, chained,
                                              cs));
@@ -168,19 +243,28 @@ int fwd_output(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs, boo
 }
 
 int bwd_chunk_states(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs, bool chained) {
+  if (m.walk) return cuda_fail(lasp::walk_span_totals(m, a->q, a->d_o, a->s, lasp::ws_walk_border(a->ws, m), true, cs));
   if (m.path == LASP_PATH_TENSOR)
     return cuda_fail(lasp::tensor_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_local_bf16(a->ws), true, chained, cs));
   return cuda_fail(lasp::simt_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_states_f32(a->ws), true, cs));
 }
 
 int bwd_scan(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs, bool chained) {
-  if (m.path == LASP_PATH_TENSOR)
+  if (m.path == LASP_PATH_TENSOR && !m.walk)
     return cuda_fail(lasp::scan_states_bf16(m, a->s, lasp::ws_local_bf16(a->ws), lasp::ws_states_bf16(a->ws, m),
                                             a->dkv_in, a->dkv_out, true, chained, cs));
-  return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_states_f32(a->ws), a->dkv_in, a->dkv_out, true, cs));
+  float* states = m.walk ? lasp::ws_walk_border(a->ws, m) : lasp::ws_states_f32(a->ws);
+  return cuda_fail(lasp::scan_states(m, a->s, states, a->dkv_in, a->dkv_out, true, cs));
 }
 
 int bwd_grads(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs, bool chained) {
+  if (m.walk) {
+    // dQ walks forward over the prefix states the forward pass left in its workspace; dK, dV walk backward
+    int st = cuda_fail(lasp::walk_bwd_dq(m, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m), a->dq, cs));
+    if (st != LASP_OK) return st;
+    return cuda_fail(lasp::walk_bwd_dkv(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->ws, m), a->dk,
+                                        a->dv, cs));
+  }
   if (m.path == LASP_PATH_TENSOR)
     return cuda_fail(lasp::tensor_bwd_grads(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_states_bf16(a->fwd_ws, m),
                                             lasp::ws_states_bf16(a->ws, m), a->dq, a->dk, a->dv, chained, cs));
@@ -216,6 +300,9 @@ int lasp_b200_forward(const lasp_problem* p, const lasp_fwd_args* a, void* strea
   int st = check_fwd(p, a, &m, true);
   if (st != LASP_OK) return st;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (fusable(m))
+    return cuda_fail(lasp::walk_fwd_fused(m, a->q, a->k, a->v, a->s, a->kv_in, a->kv_out, lasp::ws_walk_sync(a->ws),
+                                          lasp::ws_walk_totals(a->ws), lasp::ws_walk_border(a->ws, m), a->o, cs));
   const bool chained = chain_launches() && m.path == LASP_PATH_TENSOR;
   if ((st = fwd_chunk_states(m, a, cs, chained)) != LASP_OK) return st;
   if ((st = fwd_scan(m, a, cs, chained)) != LASP_OK) return st;

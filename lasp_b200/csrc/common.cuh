@@ -9,27 +9,49 @@
 
 namespace lasp {
 
-// Workspace layout (forward and backward use the same one):
-//   SIMT path  : [0, S*4)   fp32 chunk states, (b,h,nc,d,e): local states after
-//                           the chunk-state phase; the scan turns them into
-//                           prefix states in place
-//   TENSOR path: [0, S*2)   bf16 local chunk states, (b,h,nc,d,e)
-//                [S*2, S*4) bf16 prefix states written by the scan (the MMA
-//                           operand), (b,h,nc,d,e) row-major (d rows, e cols)
-// with S = b*h*nc*d*e.  The running prefix inside the scan is always fp32.
-constexpr int kSimtChunk = 64;     // the reference's block size
-constexpr int kTensorChunk = 128;  // one tcgen05 M=128 tile
+// Workspace layout (forward and backward use the same one): S*4 bytes with
+// S = b*h*nc*d*e, where nc is the number of states kept per sequence:
+//   SIMT path        : fp32 chunk states (b,h,nc,d,e), one per 64-token chunk:
+//                      local states after the chunk-state phase; the scan turns
+//                      them into prefix states in place
+//   TENSOR path, walk: one state per SPAN of `span` 128-token tiles (a few per
+//                      sequence; inside a span the state lives on chip):
+//                      [0, 4096)            words the CTAs of the fused kernels
+//                                           synchronise through (zeroed once by
+//                                           the caller, kept by the library)
+//                      [4096, 4096 + S*4)   fp32 span totals (fused kernels)
+//                      [4096 + S*4, + S*4)  fp32 states at the span borders
+//   TENSOR path, tile: [0, S*2) bf16 local states, one per 128-token tile,
+//                      [S*2, S*4) bf16 prefix states written by the scan
+// The running prefix inside the scan is always fp32.
+constexpr int kSimtChunk = 64;    // the reference's block size
+constexpr int kTensorTile = 128;  // one tcgen05 M=128 tile
 
 struct Dims {
   int b, h, n, d, e;
-  int chunk;  // tokens per chunk state
-  int nc;     // chunks per sequence
+  int chunk;  // tokens per state kept in the workspace
+  int nc;     // states per sequence
   int dtype;
   int path;
+  int walk;   // tensor path: 1 = state carried on chip along a span, 0 = one state per tile
+  int tiles;  // tensor path: 128-token tiles per sequence
+  int span;   // tensor path, walk: tiles per span (chunk = span * 128)
 };
+
+// SM count of the current device (cached per device ordinal)
+int sm_count();
 
 inline size_t state_elems(const Dims& m) { return (size_t)m.b * m.h * m.nc * m.d * m.e; }
 
+constexpr size_t kWalkSyncBytes = 4096;
+inline uint32_t* ws_walk_sync(void* ws) { return reinterpret_cast<uint32_t*>(ws); }
+inline float* ws_walk_totals(void* ws) { return reinterpret_cast<float*>(static_cast<char*>(ws) + kWalkSyncBytes); }
+inline float* ws_walk_border(void* ws, const Dims& m) {
+  return reinterpret_cast<float*>(static_cast<char*>(ws) + kWalkSyncBytes + state_elems(m) * 4);
+}
+inline const float* ws_walk_border(const void* ws, const Dims& m) {
+  return reinterpret_cast<const float*>(static_cast<const char*>(ws) + kWalkSyncBytes + state_elems(m) * 4);
+}
 inline float* ws_states_f32(void* ws) { return reinterpret_cast<float*>(static_cast<char*>(ws)); }
 inline const float* ws_states_f32(const void* ws) {
   return reinterpret_cast<const float*>(static_cast<const char*>(ws));
@@ -49,6 +71,7 @@ enum : int32_t {
   kFaultTmaWait = 1,   // a bounded wait on a TMA mbarrier ran out
   kFaultMmaWait = 2,   // a bounded wait on a tcgen05.commit mbarrier ran out
   kFaultRelayWait = 4, // a bounded wait on a peer's flag ran out (state relay)
+  kFaultFlagWait = 8,  // a bounded wait on another CTA's flag ran out (fused kernels)
 };
 cudaError_t read_fault_word(int32_t* host, bool clear, cudaStream_t st);
 // device address of the current device's fault word (for kernels in other translation units)
@@ -88,5 +111,19 @@ cudaError_t tensor_bwd_grads(const Dims& m, const void* q, const void* k, const 
                              const float* s, const __nv_bfloat16* prefix, const __nv_bfloat16* suffix, void* dq,
                              void* dk, void* dv, bool chained, cudaStream_t st);
 bool tensor_path_supported(const Dims& m);
+bool tensor_tile_path_supported(const Dims& m);
+
+// tcgen05 path with the state carried on chip (walk_kernels.cu)
+cudaError_t walk_span_totals(const Dims& m, const void* a, const void* bten, const float* s, float* totals,
+                             bool reverse, cudaStream_t st);
+cudaError_t walk_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
+                            const float* prefix, void* o, cudaStream_t st);
+cudaError_t walk_fwd_fused(const Dims& m, const void* q, const void* k, const void* v, const float* s,
+                           const float* x_in, float* x_out, uint32_t* sync, float* totals, float* prefix, void* o,
+                           cudaStream_t st);
+cudaError_t walk_bwd_dq(const Dims& m, const void* k, const void* v, const void* d_o, const float* s,
+                        const float* prefix, void* dq, cudaStream_t st);
+cudaError_t walk_bwd_dkv(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
+                         const float* s, const float* suffix, void* dk, void* dv, cudaStream_t st);
 
 }  // namespace lasp

@@ -226,12 +226,12 @@ cudaError_t state_total(const Dims& m, const float* s, const void* local, float*
                         cudaStream_t st) {
   const int de = m.d * m.e;
   dim3 grid((de / 4 + 127) / 128, m.b * m.h);
-  if (m.path == LASP_PATH_TENSOR)
+  if (m.path == LASP_PATH_TENSOR && !m.walk)
     k_state_total<__nv_bfloat16><<<grid, 128, 0, st>>>(s, static_cast<const __nv_bfloat16*>(local), total, m.h, m.n,
                                                         de, m.nc, m.chunk, reverse ? 1 : 0);
   else
-    k_state_total<float><<<grid, 128, 0, st>>>(s, static_cast<const float*>(local), total, m.h, m.n, de, m.nc, m.chunk,
-                                               reverse ? 1 : 0);
+    k_state_total<float><<<grid, 128, 0, st>>>(s, m.walk ? ws_walk_border(local, m) : static_cast<const float*>(local),
+                                               total, m.h, m.n, de, m.nc, m.chunk, reverse ? 1 : 0);
   return cudaGetLastError();
 }
 

@@ -1,0 +1,180 @@
+// Device helpers shared by the tensor-core kernels: bounded waits that report
+// through the fault word, accumulator <-> shared-memory moves with the decay
+// mask, and the enumeration of the tiles a persistent CTA walks over.
+#pragma once
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace lasp {
+namespace tc {
+
+using namespace sm100;
+
+constexpr int C = kTensorTile;  // 128 tokens per tile
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr uint32_t kNoAcc = 0xFFFFFFFFu;
+
+// bounded wait that records a fault once and makes later waits of the CTA no-ops
+__device__ __forceinline__ void wait_or_fault(uint64_t* bar, uint32_t parity, volatile int* dead, int32_t* fault,
+                                              int32_t code) {
+  if (*dead) return;
+  if (!mbar_wait(bar, parity)) {
+    *dead = 1;
+    atomicOr(fault, code);
+  }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
+  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
+}
+
+__device__ __forceinline__ float decay_pow(float sl2, int k) { return exp2f(-sl2 * (float)k); }
+
+// acc (32 columns) *= f, in tensor memory
+__device__ __forceinline__ void scale_tmem32(uint32_t taddr, float f) {
+  uint32_t r[32];
+  tmem_ld32(taddr, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * f);
+  tmem_st32(taddr, r);
+}
+
+// tile[row][col0 .. col0+31] = bf16(acc1 + f * acc2) into a swizzled staging tile of C rows
+// (acc2 skipped when taddr2 == kNoAcc); a TMA store then moves the tile out
+__device__ __forceinline__ void stage_row32(uint32_t taddr1, uint32_t taddr2, float f, uint8_t* tile, int row,
+                                            int col0) {
+  uint32_t a[32];
+  tmem_ld32(taddr1, a);
+  if (taddr2 != kNoAcc) {
+    uint32_t b[32];
+    tmem_ld32(taddr2, b);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) a[j] = __float_as_uint(fmaf(f, __uint_as_float(b[j]), __uint_as_float(a[j])));
+  } else {
+    tmem_ld_wait();
+  }
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    uint4 v = make_uint4(pack_bf16(__uint_as_float(a[j]), __uint_as_float(a[j + 1])),
+                         pack_bf16(__uint_as_float(a[j + 2]), __uint_as_float(a[j + 3])),
+                         pack_bf16(__uint_as_float(a[j + 4]), __uint_as_float(a[j + 5])),
+                         pack_bf16(__uint_as_float(a[j + 6]), __uint_as_float(a[j + 7])));
+    *reinterpret_cast<uint4*>(tile + tile_offset(row, col0 + j, C)) = v;
+  }
+}
+
+// Tensor-memory accumulator (32 columns at `taddr`, this thread's lane = row) ->
+// decay-masked bf16 in a K-major swizzled tile:
+//   out[row][col] = [row >= col] lambda^(row-col) acc[col].
+// Per group of eight columns the factor is built from the group's right-most unmasked column
+// leftwards by repeated multiplication with lambda (short independent chains), so it can only
+// underflow towards the far columns.  The 32 rows of a warp are `row0 .. row0+31`: groups wholly
+// below the diagonal for every row of the warp need no comparisons, groups wholly above it are zero.
+__device__ __forceinline__ void masked_store32(uint32_t taddr, uint8_t* tile, int row, int col0, float sl2,
+                                               float lam) {
+  const int row0 = row & ~31;
+  if (col0 > row0 + 31) {   // the whole block is above the diagonal (same for every lane of the warp)
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      *reinterpret_cast<uint4*>(tile + tile_offset(row, col0 + 8 * g, C)) = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  uint32_t r[32];
+  tmem_ld32(taddr, r);
+  float f[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) f[g] = decay_pow(sl2, row - min(row, col0 + 8 * g + 7));
+  tmem_ld_wait();
+  if (col0 + 31 <= row0) {  // the whole block is below the diagonal
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float m[8];
+#pragma unroll
+      for (int j = 7; j >= 0; --j) {
+        m[j] = __uint_as_float(r[8 * g + j]) * f[g];
+        f[g] *= lam;
+      }
+      *reinterpret_cast<uint4*>(tile + tile_offset(row, col0 + 8 * g, C)) =
+          make_uint4(pack_bf16(m[0], m[1]), pack_bf16(m[2], m[3]), pack_bf16(m[4], m[5]), pack_bf16(m[6], m[7]));
+    }
+    return;
+  }
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float m[8];
+#pragma unroll
+    for (int j = 7; j >= 0; --j) {
+      const bool live = (col0 + 8 * g + j) <= row;
+      m[j] = live ? __uint_as_float(r[8 * g + j]) * f[g] : 0.f;
+      f[g] = live ? f[g] * lam : f[g];
+    }
+    *reinterpret_cast<uint4*>(tile + tile_offset(row, col0 + 8 * g, C)) =
+        make_uint4(pack_bf16(m[0], m[1]), pack_bf16(m[2], m[3]), pack_bf16(m[4], m[5]), pack_bf16(m[6], m[7]));
+  }
+}
+
+// Multiplies CHUNKS 16-byte pieces of row `row` of a swizzled tile of C rows by w, in place, starting
+// at piece `first` (pieces are counted slab by slab; a row keeps its pieces under the swizzle, so the
+// physical position inside the row does not matter).  `lane` rotates the order to spread the banks.
+template <int CHUNKS>
+__device__ __forceinline__ void scale_row_pieces(uint8_t* tile, int row, int first, float w, int lane) {
+  static_assert((CHUNKS & (CHUNKS - 1)) == 0, "a power of two");
+  uint4 v[CHUNKS];
+  uint4* p[CHUNKS];
+#pragma unroll
+  for (int q = 0; q < CHUNKS; ++q) {   // all loads first: their latencies overlap
+    const int piece = first + ((q + lane) & (CHUNKS - 1));
+    p[q] = reinterpret_cast<uint4*>(tile + (piece >> 3) * C * 128 + row * 128 + (piece & 7) * 16);
+    v[q] = *p[q];
+  }
+#pragma unroll
+  for (int q = 0; q < CHUNKS; ++q) {
+    uint32_t* u = reinterpret_cast<uint32_t*>(&v[q]);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u[t]));
+      u[t] = pack_bf16(f.x * w, f.y * w);
+    }
+    *p[q] = v[q];
+  }
+}
+
+// The work of a persistent CTA: items blockIdx.x, blockIdx.x + gridDim.x, ...; an item is one span of
+// consecutive tiles of one (batch, head) sequence, walked first to last tile or last to first.
+struct TileWalk {
+  int items, nspans, span, tiles, stride;
+  bool backwards;
+  int it, bh, t, t0, t1;  // current item, its sequence, current tile, the item's tile range [t0, t1)
+
+  __device__ __forceinline__ bool load() {
+    if (it >= items) return false;
+    bh = it / nspans;
+    const int sp = it - bh * nspans;
+    t0 = sp * span;
+    t1 = min(tiles, t0 + span);
+    t = backwards ? t1 - 1 : t0;
+    return true;
+  }
+  __device__ __forceinline__ bool start(int first_item, int item_stride) {
+    it = first_item;
+    stride = item_stride;
+    return load();
+  }
+  __device__ __forceinline__ bool next() {
+    if (backwards ? (--t >= t0) : (++t < t1)) return true;
+    it += stride;
+    return load();
+  }
+  __device__ __forceinline__ bool first_of_item() const { return backwards ? t == t1 - 1 : t == t0; }
+  __device__ __forceinline__ bool last_of_item() const { return backwards ? t == t0 : t == t1 - 1; }
+};
+
+}  // namespace tc
+}  // namespace lasp

@@ -54,7 +54,7 @@ namespace {
 
 using namespace sm100;
 
-constexpr int C = kTensorChunk;  // 128 tokens per tile
+constexpr int C = kTensorTile;  // 128 tokens per tile
 
 // bounded wait that records a fault once and makes later waits of the CTA no-ops
 __device__ __forceinline__ void wait_or_fault(uint64_t* bar, uint32_t parity, volatile int* dead, int32_t code) {
@@ -726,18 +726,6 @@ __global__ void __launch_bounds__(320, 1) k_tc_bwd_grads(
 }
 
 
-// SM count of the current device (cached per device ordinal)
-int sm_count() {
-  static int cached[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (!cached[dev]) {
-    int v = 0;
-    cached[dev] = (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) ? v : 148;
-  }
-  return cached[dev];
-}
-
 bool chunk_states_v2_enabled() {
   static const bool on = [] {
     const char* v = getenv("LASP_B200_CHUNK_STATES_V2");
@@ -895,20 +883,9 @@ cudaError_t launch_bwd_grads(const Dims& m, const void* q, const void* k, const 
 
 }  // namespace
 
-// d = e = 128 is verified against the oracle on B200.  The 64-wide
-// instantiations are built but only selected when LASP_B200_TENSOR_HEAD64=1
-// until they have had the same verification.
-static bool head64_enabled() {
-  static const bool on = [] {
-    const char* v = getenv("LASP_B200_TENSOR_HEAD64");
-    return v && v[0] == '1';
-  }();
-  return on;
-}
-
-bool tensor_path_supported(const Dims& m) {
-  const bool dims_ok = (m.d == 128 && m.e == 128) ||
-                       (head64_enabled() && (m.d == 64 || m.d == 128) && (m.e == 64 || m.e == 128));
+// the per-tile kernels of this file: full tiles only
+bool tensor_tile_path_supported(const Dims& m) {
+  const bool dims_ok = (m.d == 64 || m.d == 128) && (m.e == 64 || m.e == 128);
   return m.dtype == LASP_BF16 && dims_ok && m.n % C == 0 && (long long)m.b * m.h * m.n < (1LL << 31);
 }
 

@@ -1,0 +1,1019 @@
+// Tensor-core path (tcgen05 MMAs, accumulators in tensor memory, operands staged by TMA) with the
+// running KV / dKV state kept ON CHIP.  bf16 inputs, fp32 accumulation, one rounding on store.
+//
+// A sequence of one (batch, head) is cut into 128-token tiles and the tiles into spans of `span`
+// consecutive tiles; a span is the unit of work of a persistent CTA.  Per direction:
+//
+//   k_span_totals   T_span = sum over the span's tokens of decay * a_j b_j^T  (a,b = k,v or q,do)
+//   (scan over the few span totals of a sequence: k_scan of simt_kernels.cu, seeded with the rank's
+//    incoming state; gives every span its fp32 state at the span border)
+//   k_walk_out      walks a span first to last tile with the d x e state in registers (fp32) and in
+//                   shared memory (bf16 MMA operand):  OUT = (X Y^T . M) Z + diag(lambda^r) X op(P),
+//                   then P <- lambda^C P + K^T diag(w) V.  Forward: (X,Y,Z,OUT) = (Q,K,V,O), op(P)=P;
+//                   the same kernel gives dQ with (X,Y,Z,OUT) = (dO,V,K,dQ), op(P)=P^T.
+//   k_walk_dkv      walks a span last to first tile with the suffix state Dn on chip: dK, dV.
+//
+// So K and V (Q and dO) are read twice per direction and nothing else is: no per-tile state is written
+// to or read from global memory.  Every tile in shared memory is in the swizzled slab format of
+// sm100.cuh; all buffers are 32 KB so that a tile's buffer can be reused for the decay-masked score
+// tile and for the staging tile of the TMA store.  All waits are bounded (see tc_common.cuh).
+#include <stdio.h>
+#include <stdlib.h>
+
+#include "tc_common.cuh"
+
+namespace lasp {
+
+namespace {
+
+using namespace tc;
+
+#ifdef LASP_TRACE
+__device__ long long g_trace[160 * 64];
+#define TRACE(slot) do { if (blockIdx.x < 160 && (slot) < 64) g_trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(slot) do {} while (0)
+#endif
+
+constexpr int kBuf = 32768;       // one shared-memory buffer: a 128 x 128 bf16 tile
+constexpr int kWorkers = 256;     // warps 2..9
+
+// ---------------------------------------------------------------------------
+// span totals: totals[item][i][j] = sum_c w_c A[c][i] B[c][j] over the span's tokens
+//   forward  (A,B) = (K,V):  w = lambda^(span end - position)      (decayed to the end of the span)
+//   backward (A,B) = (Q,dO): w = lambda^(position - span start)    (decayed to the start of the span)
+// Ten warps: warp 0 producer (three-stage ring of A,B tiles), warp 1 tensor-core issuer (accumulator
+// double buffered over items), warps 2-5 scale the rows of A in place, warps 6-9 write the totals.
+// ---------------------------------------------------------------------------
+template <int D, int E>
+__global__ void __launch_bounds__(320, 1) k_span_totals(const __grid_constant__ CUtensorMap map_a,
+                                                        const __grid_constant__ CUtensorMap map_b,
+                                                        const float* __restrict__ s, float* __restrict__ totals,
+                                                        int h, int n, int tiles, int span, int nspans, int items,
+                                                        int reverse, int32_t* fault) {
+  constexpr int kStages = 3;
+  constexpr int kA = C * D * 2, kB = C * E * 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  // per stage: A then B (with D = 64 the M = 128 MMA reads on from A into B, which is valid memory)
+  __shared__ uint64_t full[kStages], scaled[kStages], empty[kStages], acc_full[2], acc_free[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int dead;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    dead = 0;
+    for (int j = 0; j < kStages; ++j) {
+      mbar_init(&full[j], 1);
+      mbar_init(&scaled[j], 128);
+      mbar_init(&empty[j], 1);
+    }
+    for (int j = 0; j < 2; ++j) {
+      mbar_init(&acc_full[j], 1);
+      mbar_init(&acc_free[j], 128);
+    }
+    fence_mbar_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+  }
+  if (warp == 2) tmem_alloc(&tmem_slot, 256);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  TileWalk w{items, nspans, span, tiles, 0, false};
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int g = 0;
+      for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++g) {
+        const int j = g % kStages, use = g / kStages;
+        if (use >= 1) wait_or_fault(&empty[j], (use - 1) & 1, &dead, fault, kFaultMmaWait);
+        uint8_t* sa = smem + j * (kA + kB);
+        mbar_expect_tx(&full[j], kA + kB);
+        tma_load_4d(sa, &map_a, &full[j], 0, w.t * C, 0, w.bh);
+        tma_load_4d(sa + kA, &map_b, &full[j], 0, w.t * C, 0, w.bh);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int g = 0, li = -1;
+      for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++g) {
+        const int j = g % kStages, use = g / kStages;
+        if (w.first_of_item()) {
+          ++li;
+          if (li >= 2) wait_or_fault(&acc_free[li & 1], ((li >> 1) - 1) & 1, &dead, fault, kFaultMmaWait);
+        }
+        wait_or_fault(&scaled[j], use & 1, &dead, fault, kFaultTmaWait);
+        tc_fence_after_sync();
+        uint8_t* sa = smem + j * (kA + kB);
+        umma_gemm(tmem + 128 * (li & 1), Operand{smem_u32(sa), C, true}, Operand{smem_u32(sa + kA), C, true}, E, C / 16,
+                  !w.first_of_item());
+        umma_commit(&empty[j]);
+        if (w.last_of_item()) umma_commit(&acc_full[li & 1]);
+      }
+    }
+  } else if (warp < 6) {
+    const int row = tid - 64;  // the token of the tile this thread scales
+    int g = 0;
+    for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++g) {
+      const int j = g % kStages, use = g / kStages;
+      const float sl2 = s[w.bh % h] * kLog2e;
+      const int pos = w.t * C + row;
+      const int dist = reverse ? pos - w.t0 * C : min(w.t1 * C, n) - pos;
+      const float wt = decay_pow(sl2, max(dist, 0));  // rows past the end of the sequence are zero anyway
+      wait_or_fault(&full[j], use & 1, &dead, fault, kFaultTmaWait);
+      scale_row_pieces<D / 8>(smem + j * (kA + kB), row, 0, wt, lane);
+      fence_async_smem();
+      mbar_arrive(&scaled[j]);
+    }
+  } else {
+    const int row = (warp & 3) * 32 + lane;  // tensor-memory lane = row of the state; warps 6..9 -> quarters 2,3,0,1
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    int li = -1;
+    for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next()) {
+      if (!w.last_of_item()) continue;
+      ++li;
+      wait_or_fault(&acc_full[li & 1], (li >> 1) & 1, &dead, fault, kFaultMmaWait);
+      tc_fence_after_sync();
+      if (row < D) {
+        float* out = totals + ((size_t)w.it * D + row) * E;
+#pragma unroll
+        for (int c0 = 0; c0 < E; c0 += 32) {
+          uint32_t a[32];
+          tmem_ld32(tmem + 128 * (li & 1) + lane_base + c0, a);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 32; q += 4)
+            *reinterpret_cast<float4*>(out + c0 + q) = make_float4(__uint_as_float(a[q]), __uint_as_float(a[q + 1]),
+                                                                   __uint_as_float(a[q + 2]), __uint_as_float(a[q + 3]));
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&acc_free[li & 1]);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) tmem_dealloc(tmem, 256);
+}
+
+// ---------------------------------------------------------------------------
+// flags between the CTAs of one launch (fused kernels)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_volatile_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// spins until *flag == want or `limit` clocks pass
+__device__ __forceinline__ bool wait_flag_eq(const uint32_t* flag, uint32_t want, long long limit) {
+  if (ld_volatile_u32(flag) == want) return true;
+  const long long t0 = clock64();
+  while (ld_volatile_u32(flag) != want) {
+    if (clock64() - t0 > limit) return false;
+  }
+  return true;
+}
+
+struct WalkArgs {
+  const float* s;
+  const float* p0;     // not fused: fp32 state of every span at its border, [items][D][E] (from the scan)
+  float* p0_save;      // fused: where the border states are kept for the backward pass (may be NULL)
+  float* totals;       // fused: span totals [items][D][E], exchanged between the CTAs of the launch
+  uint32_t* sync;      // fused: [0] launch counter, [1] CTAs done, [kSyncFlags + item] "total written" flags
+  const float* x_in;   // fused: incoming rank state (b,h,d,e) or NULL
+  float* x_out;        // fused: outgoing rank state (b,h,d,e) or NULL
+  int h, n, tiles, span, nspans, items;
+  int all_totals;      // fused: the last span of a sequence computes its total too
+  long long wait_clocks;
+  int32_t* fault;
+};
+constexpr int kSyncFlags = 32;
+
+// bf16 image of this thread's part of the state (row `row`, columns [col0, col0 + N)) in the operand tile
+template <int N>
+__device__ __forceinline__ void write_state_operand(uint8_t* tile, int rows, int row, int col0, const float (&P)[N]) {
+#pragma unroll
+  for (int j = 0; j < N; j += 8)
+    *reinterpret_cast<uint4*>(tile + tile_offset(row, col0 + j, rows)) =
+        make_uint4(pack_bf16(P[j], P[j + 1]), pack_bf16(P[j + 2], P[j + 3]), pack_bf16(P[j + 4], P[j + 5]),
+                   pack_bf16(P[j + 6], P[j + 7]));
+}
+
+// ---------------------------------------------------------------------------
+// walk, first to last tile:  OUT = (X Y^T . M) Z + diag(lambda^r) X op(P);  P <- lambda^C P + K^T diag(w) V
+//
+//   DQ = false: X,Y = Q,K (width D), Z,OUT = V,O (width E), op(P) = P
+//   DQ = true : X,Y = dO,V (width E), Z,OUT = K,dQ (width D), op(P) = P^T
+// P is the d x e state in both: fp32 in the registers of the eight worker warps (thread = one row and
+// half of the columns) and bf16 in shared memory as the operand of X op(P).
+//
+// Shared memory: X, Y, Z double buffered and the state operand, seven 32 KB buffers.  A buffer's life
+// inside a tile:  X: tile -> (after S, O2)  masked scores S_m -> free after O1
+//                 Y: tile -> (after S) rows scaled in place -> free after L -> staging tile of OUT
+//                 Z: tile -> free after L and O1
+// Tensor memory: S (two buffers; O1 = S_m Z is written over S), O2 = X op(P), L = the state update.
+//   warp 0 (one lane)  producer: loads, and the TMA stores of the finished staging tiles
+//   warp 1 (one lane)  tensor-core issuer
+//   warps 2-9          mask, row scaling, state update, epilogue
+//
+// FUSED = false: the state of every span at its border comes from the scan (a.p0).
+// FUSED = true : one launch does everything.  With more than one span per sequence every CTA has
+//   exactly one span (a cooperative launch, all CTAs resident).  It first sums its own span,
+//   T = sum_c lambda^(span end - c) k_c v_c^T, streaming K and V once through the Y and Z buffers, writes
+//   T to global memory and raises a flag; then it adds up the totals of the spans before it (and the
+//   incoming rank state) with their decays - that is its border state - and walks.  The K and V tiles
+//   are read again by the walk (they are in L2 by then).  The last span of a sequence needs no total
+//   unless a.all_totals; the outgoing rank state is the state after the last tile of the last span.
+// ---------------------------------------------------------------------------
+template <int D, int E, bool DQ, bool FUSED>
+__global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUtensorMap map_x,
+                                                     const __grid_constant__ CUtensorMap map_y,
+                                                     const __grid_constant__ CUtensorMap map_z,
+                                                     const __grid_constant__ CUtensorMap map_out,
+                                                     const __grid_constant__ WalkArgs a) {
+  static_assert(!(DQ && FUSED), "dQ walks over states the forward pass kept");
+  constexpr int WX = DQ ? E : D;  // width of X and Y
+  constexpr int WZ = DQ ? D : E;  // width of Z and OUT
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* sx[2] = {smem, smem + kBuf};
+  uint8_t* sy[2] = {smem + 2 * kBuf, smem + 3 * kBuf};
+  uint8_t* sz[2] = {smem + 4 * kBuf, smem + 5 * kBuf};
+  uint8_t* sp = smem + 6 * kBuf;
+  __shared__ uint64_t x_full[2], y_full[2], z_full[2], s_full[2], sm_ready[2], o_full[2], t_free[2], staged[2];
+  __shared__ uint64_t p_ready, l_free, o2_free, ys_ready, o2_full, l_full;
+  __shared__ uint64_t ring_full[2], ring_scaled[2], ring_empty[2], sum_done;   // the span-total phase
+  __shared__ uint32_t tmem_slot, step_s;
+  __shared__ int dead;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int32_t* fault = a.fault;
+  if (tid == 0) {
+    dead = 0;
+    for (int p = 0; p < 2; ++p) {
+      mbar_init(&x_full[p], 1);
+      mbar_init(&y_full[p], 1);
+      mbar_init(&z_full[p], 1);
+      mbar_init(&s_full[p], 1);
+      mbar_init(&sm_ready[p], kWorkers);
+      mbar_init(&o_full[p], 1);
+      mbar_init(&t_free[p], kWorkers);
+      mbar_init(&staged[p], kWorkers);
+      mbar_init(&ring_full[p], 1);
+      mbar_init(&ring_scaled[p], kWorkers);
+      mbar_init(&ring_empty[p], 1);
+    }
+    mbar_init(&p_ready, kWorkers);
+    mbar_init(&l_free, kWorkers);
+    mbar_init(&o2_free, kWorkers);
+    mbar_init(&ys_ready, kWorkers);
+    mbar_init(&o2_full, 1);
+    mbar_init(&l_full, 1);
+    mbar_init(&sum_done, 1);
+    fence_mbar_init();
+    prefetch_tensormap(&map_x);
+    prefetch_tensormap(&map_y);
+    prefetch_tensormap(&map_z);
+    prefetch_tensormap(&map_out);
+    if constexpr (FUSED) step_s = a.nspans > 1 ? ld_volatile_u32(a.sync) + 1 : 0;
+  }
+  if (warp == 2) tmem_alloc(&tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  if (tid == 64) TRACE(0);
+  const uint32_t t_s[2] = {tmem, tmem + 128}, t_o2 = tmem + 256, t_l = tmem + 384;
+  TileWalk w{a.items, a.nspans, a.span, a.tiles, 0, false};
+  // the span-total phase: only with several spans per sequence, and then this CTA has one span
+  bool sums = false;
+  int sum_t0 = 0, sum_t1 = 0, my_bh = 0, my_sp = 0;
+  if constexpr (FUSED) {
+    if (a.nspans > 1 && w.start(blockIdx.x, gridDim.x)) {
+      my_bh = w.bh;
+      my_sp = w.it - w.bh * a.nspans;
+      sum_t0 = w.t0;
+      sum_t1 = w.t1;
+      sums = my_sp < a.nspans - 1 || a.all_totals;
+    }
+  }
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int x_issued = 0;
+      if (sums) {
+        // X of the first two tiles of the walk can come in during the sums
+        for (bool ok = w.start(blockIdx.x, gridDim.x); ok && x_issued < 2; ok = w.next(), ++x_issued) {
+          mbar_expect_tx(&x_full[x_issued], C * WX * 2);
+          tma_load_4d(sx[x_issued], &map_x, &x_full[x_issued], 0, w.t * C, 0, w.bh);
+        }
+        for (int t = sum_t0, g = 0; t < sum_t1; ++t, ++g) {
+          const int j = g & 1;
+          if (g >= 2) wait_or_fault(&ring_empty[j], ((g >> 1) - 1) & 1, &dead, fault, kFaultMmaWait);
+          mbar_expect_tx(&ring_full[j], C * (WX + WZ) * 2);
+          tma_load_4d(sy[j], &map_y, &ring_full[j], 0, t * C, 0, my_bh);
+          tma_load_4d(sz[j], &map_z, &ring_full[j], 0, t * C, 0, my_bh);
+        }
+        wait_or_fault(&sum_done, 0, &dead, fault, kFaultMmaWait);   // the MMAs have read every ring stage
+      }
+      int i = 0;
+      int out_row[2] = {0, 0}, out_bh[2] = {0, 0};
+      for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++i) {
+        const int p = i & 1, u = i >> 1;
+        if (i >= 2) wait_or_fault(&o_full[p], (u - 1) & 1, &dead, fault, kFaultMmaWait);  // X, Z of tile i-2 are read
+        if (i >= x_issued) {
+          mbar_expect_tx(&x_full[p], C * WX * 2);
+          tma_load_4d(sx[p], &map_x, &x_full[p], 0, w.t * C, 0, w.bh);
+        }
+        mbar_expect_tx(&z_full[p], C * WZ * 2);
+        tma_load_4d(sz[p], &map_z, &z_full[p], 0, w.t * C, 0, w.bh);
+        if (i >= 2) {
+          // the output of tile i-2 is staged in Y's buffer: store it, then reuse the buffer
+          wait_or_fault(&staged[p], (u - 1) & 1, &dead, fault, kFaultMmaWait);
+          tma_store_4d(&map_out, sy[p], 0, out_row[p], 0, out_bh[p]);
+          bulk_commit();
+          bulk_wait_read<0>();
+        }
+        mbar_expect_tx(&y_full[p], C * WX * 2);
+        tma_load_4d(sy[p], &map_y, &y_full[p], 0, w.t * C, 0, w.bh);
+        out_row[p] = w.t * C;
+        out_bh[p] = w.bh;
+      }
+      for (int j = (i >= 2 ? i - 2 : 0); j < i; ++j) {   // the last two tiles
+        const int p = j & 1, u = j >> 1;
+        wait_or_fault(&staged[p], u & 1, &dead, fault, kFaultMmaWait);
+        tma_store_4d(&map_out, sy[p], 0, out_row[p], 0, out_bh[p]);
+        bulk_commit();
+      }
+      bulk_wait_all<0>();
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      if (sums) {
+        for (int t = sum_t0, g = 0; t < sum_t1; ++t, ++g) {
+          const int j = g & 1;
+          wait_or_fault(&ring_scaled[j], (g >> 1) & 1, &dead, fault, kFaultTmaWait);
+          tc_fence_after_sync();
+          umma_gemm(t_l, Operand{smem_u32(sy[j]), C, true}, Operand{smem_u32(sz[j]), C, true}, E, C / 16, g > 0);
+          umma_commit(&ring_empty[j]);
+        }
+        umma_commit(&sum_done);
+      }
+      int total = 0;
+      for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next()) ++total;
+      // Issue order: S of tile i+1 goes out before O1 of tile i, so that the score chain of the next
+      // tile (S -> mask) never waits for this tile's mask; the state chain (row scaling -> L -> update
+      // -> O2 of the next tile) is issued as soon as its inputs exist.
+      if (total > 0) {
+        wait_or_fault(&x_full[0], 0, &dead, fault, kFaultTmaWait);
+        wait_or_fault(&y_full[0], 0, &dead, fault, kFaultTmaWait);
+        tc_fence_after_sync();
+        umma_gemm(t_s[0], Operand{smem_u32(sx[0]), C, false}, Operand{smem_u32(sy[0]), C, false}, C, WX / 16, false);
+        umma_commit(&s_full[0]);
+      }
+      for (int i = 0; i < total; ++i) {
+        const int p = i & 1, ph = (i >> 1) & 1, one = i & 1;
+        // O2 = X op(P): needs this tile's state operand and the accumulator drained by the previous epilogue
+        wait_or_fault(&p_ready, one, &dead, fault, kFaultMmaWait);
+        if (i >= 1) wait_or_fault(&o2_free, one ^ 1, &dead, fault, kFaultMmaWait);
+        TRACE(32 + i * 5 + 0);
+        tc_fence_after_sync();
+        if constexpr (!DQ)  // X P: the state tile as [K = d rows] x [N = e columns]
+          umma_gemm(t_o2, Operand{smem_u32(sx[p]), C, false}, Operand{smem_u32(sp), D, true}, E, D / 16, false);
+        else                // X P^T: the state tile as [N = d rows] x [K = e columns]
+          umma_gemm(t_o2, Operand{smem_u32(sx[p]), C, false}, Operand{smem_u32(sp), D, false}, D, E / 16, false);
+        umma_commit(&o2_full);
+        // L = K^T diag(w) V (d x e), the scaled rows being Y's
+        wait_or_fault(&ys_ready, one, &dead, fault, kFaultMmaWait);
+        wait_or_fault(&z_full[p], ph, &dead, fault, kFaultTmaWait);
+        if (i >= 1) wait_or_fault(&l_free, one ^ 1, &dead, fault, kFaultMmaWait);
+        TRACE(32 + i * 5 + 1);
+        tc_fence_after_sync();
+        if constexpr (!DQ)
+          umma_gemm(t_l, Operand{smem_u32(sy[p]), C, true}, Operand{smem_u32(sz[p]), C, true}, E, C / 16, false);
+        else
+          umma_gemm(t_l, Operand{smem_u32(sz[p]), C, true}, Operand{smem_u32(sy[p]), C, true}, E, C / 16, false);
+        umma_commit(&l_full);
+        // S of the next tile goes out before O1 of this one when its inputs are already there (the usual
+        // case), so that the next tile's mask never waits; otherwise O1 first
+        const int q = (i + 1) & 1, uq = (i + 1) >> 1;
+        bool next_s = i + 1 < total;
+        if (next_s && mbar_test_wait(&x_full[q], uq & 1) && mbar_test_wait(&y_full[q], uq & 1) &&
+            (i + 1 < 2 || mbar_test_wait(&t_free[q], (uq - 1) & 1))) {
+          tc_fence_after_sync();
+          umma_gemm(t_s[q], Operand{smem_u32(sx[q]), C, false}, Operand{smem_u32(sy[q]), C, false}, C, WX / 16, false);
+          umma_commit(&s_full[q]);
+          next_s = false;
+        }
+        TRACE(32 + i * 5 + 2);
+        // O1 = S_m Z over S's columns
+        wait_or_fault(&sm_ready[p], ph, &dead, fault, kFaultMmaWait);
+        TRACE(32 + i * 5 + 3);
+        tc_fence_after_sync();
+        umma_gemm(t_s[p], Operand{smem_u32(sx[p]), C, false}, Operand{smem_u32(sz[p]), C, true}, WZ, C / 16, false);
+        umma_commit(&o_full[p]);
+        if (next_s) {
+          wait_or_fault(&x_full[q], uq & 1, &dead, fault, kFaultTmaWait);
+          wait_or_fault(&y_full[q], uq & 1, &dead, fault, kFaultTmaWait);
+          if (i + 1 >= 2) wait_or_fault(&t_free[q], (uq - 1) & 1, &dead, fault, kFaultMmaWait);
+          tc_fence_after_sync();
+          umma_gemm(t_s[q], Operand{smem_u32(sx[q]), C, false}, Operand{smem_u32(sy[q]), C, false}, C, WX / 16, false);
+          umma_commit(&s_full[q]);
+        }
+      }
+    }
+  } else {
+    const int cw = warp - 2;                     // 0..7
+    const int row = (warp & 3) * 32 + lane;      // tensor-memory lane quarter of this warp
+    const int half = cw >> 2;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    constexpr int kHalfE = E / 2;
+    float P[kHalfE];  // this thread's part of the state: row `row`, columns [half * E/2, (half+1) * E/2)
+    float sl2 = 0.f, lam = 1.f;
+    if (sums) {
+      // ---- this span's total, written where the CTAs of the later spans find it
+      sl2 = a.s[my_bh % a.h] * kLog2e;
+      const int span_end = min(sum_t1 * C, a.n);
+      for (int t = sum_t0, g = 0; t < sum_t1; ++t, ++g) {
+        const int j = g & 1;
+        wait_or_fault(&ring_full[j], (g >> 1) & 1, &dead, fault, kFaultTmaWait);
+        scale_row_pieces<WX / 16>(sy[j], row, half * (WX / 16), decay_pow(sl2, max(span_end - (t * C + row), 0)), lane);
+        fence_async_smem();
+        mbar_arrive(&ring_scaled[j]);
+      }
+      wait_or_fault(&sum_done, 0, &dead, fault, kFaultMmaWait);
+      tc_fence_after_sync();
+      if (row < D) {
+        float* out = a.totals + ((size_t)blockIdx.x * D + row) * E + half * kHalfE;
+#pragma unroll
+        for (int c0 = 0; c0 < kHalfE; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(t_l + lane_base + half * kHalfE + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 32; q += 4)
+            *reinterpret_cast<float4*>(out + c0 + q) = make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]),
+                                                                   __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
+        }
+      }
+      __threadfence();
+      tc_fence_before_sync();
+      named_sync(1, kWorkers);
+      if (tid == 64) st_volatile_u32(a.sync + kSyncFlags + blockIdx.x, step_s);
+    }
+    int i = 0;
+    for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++i) {
+      const int p = i & 1, ph = (i >> 1) & 1, one = i & 1;
+      const int len = min(C, a.n - w.t * C);     // tokens really in the tile
+      if (w.first_of_item()) {
+        sl2 = a.s[w.bh % a.h] * kLog2e;
+        lam = exp2f(-sl2);
+        // the state at the span border; the O2 MMA that read the operand tile of the previous item has
+        // completed (its o2_full was waited for)
+        if constexpr (!FUSED) {
+          if (row < D) {
+            const float4* src =
+                reinterpret_cast<const float4*>(a.p0 + ((size_t)w.it * D + row) * E + half * kHalfE);
+#pragma unroll
+            for (int j = 0; j < kHalfE / 4; ++j) {
+              const float4 v = src[j];
+              P[4 * j] = v.x, P[4 * j + 1] = v.y, P[4 * j + 2] = v.z, P[4 * j + 3] = v.w;
+            }
+          }
+        } else {
+          const int sp_idx = w.it - w.bh * a.nspans;
+          const size_t mine = (size_t)row * E + half * kHalfE;
+          // incoming rank state, decayed from the first token of the sequence to the first of the span
+          if (a.x_in != nullptr && row < D) {
+            const float dec = decay_pow(sl2, w.t0 * C);
+            const float4* src = reinterpret_cast<const float4*>(a.x_in + (size_t)w.bh * D * E + mine);
+#pragma unroll
+            for (int j = 0; j < kHalfE / 4; ++j) {
+              const float4 v = src[j];
+              P[4 * j] = dec * v.x, P[4 * j + 1] = dec * v.y, P[4 * j + 2] = dec * v.z, P[4 * j + 3] = dec * v.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < kHalfE; ++j) P[j] = 0.f;
+          }
+          // totals of the spans before this one (each decayed to its own end)
+          for (int j = 0; j < sp_idx; ++j) {
+            if (tid == 64 && !dead) {
+              if (!wait_flag_eq(a.sync + kSyncFlags + w.bh * a.nspans + j, step_s, a.wait_clocks)) {
+                dead = 1;
+                atomicOr(fault, kFaultFlagWait);
+              }
+            }
+            named_sync(1, kWorkers);
+            if (row < D) {
+              const float dec = decay_pow(sl2, (sp_idx - 1 - j) * a.span * C);
+              const float4* src =
+                  reinterpret_cast<const float4*>(a.totals + (size_t)(w.bh * a.nspans + j) * D * E + mine);
+#pragma unroll
+              for (int q = 0; q < kHalfE / 4; ++q) {
+                const float4 v = __ldcg(src + q);
+                P[4 * q] = fmaf(dec, v.x, P[4 * q]), P[4 * q + 1] = fmaf(dec, v.y, P[4 * q + 1]);
+                P[4 * q + 2] = fmaf(dec, v.z, P[4 * q + 2]), P[4 * q + 3] = fmaf(dec, v.w, P[4 * q + 3]);
+              }
+            }
+          }
+          if (a.p0_save != nullptr && row < D) {
+            float4* dst = reinterpret_cast<float4*>(a.p0_save + (size_t)w.it * D * E + mine);
+#pragma unroll
+            for (int q = 0; q < kHalfE / 4; ++q) dst[q] = make_float4(P[4 * q], P[4 * q + 1], P[4 * q + 2], P[4 * q + 3]);
+          }
+        }
+        if (row < D) write_state_operand<kHalfE>(sp, D, row, half * kHalfE, P);
+        fence_async_smem();
+        mbar_arrive(&p_ready);
+      }
+      if (tid == 64) TRACE(1 + i * 6 + 0);
+      wait_or_fault(&s_full[p], ph, &dead, fault, kFaultMmaWait);
+      wait_or_fault(&y_full[p], ph, &dead, fault, kFaultTmaWait);  // completed long ago: makes Y's bytes visible here
+      if (tid == 64) TRACE(1 + i * 6 + 1);
+      tc_fence_after_sync();
+      // state chain first: scale Y's rows so that L can run under the mask
+      scale_row_pieces<WX / 16>(sy[p], row, half * (WX / 16), decay_pow(sl2, max(len - row, 0)), lane);
+      fence_async_smem();
+      mbar_arrive(&ys_ready);
+      // X is overwritten by the masked scores: O2 must have read it
+      wait_or_fault(&o2_full, one, &dead, fault, kFaultMmaWait);
+      if (tid == 64) TRACE(1 + i * 6 + 2);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int col0 = half * 64 + cc * 32;
+        masked_store32(t_s[p] + lane_base + col0, sx[p], row, col0, sl2, lam);
+      }
+      fence_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&sm_ready[p]);
+      if (tid == 64) TRACE(1 + i * 6 + 3);
+      // state: P <- lambda^len P + L
+      wait_or_fault(&l_full, one, &dead, fault, kFaultMmaWait);
+      tc_fence_after_sync();
+      if (row < D) {
+        const float lam_c = decay_pow(sl2, len);
+#pragma unroll
+        for (int c0 = 0; c0 < kHalfE; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(t_l + lane_base + half * kHalfE + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) P[c0 + j] = fmaf(lam_c, P[c0 + j], __uint_as_float(r[j]));
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&l_free);
+      if (!w.last_of_item()) {
+        if (row < D) write_state_operand<kHalfE>(sp, D, row, half * kHalfE, P);
+        fence_async_smem();
+        mbar_arrive(&p_ready);
+      } else if constexpr (FUSED) {
+        // the state after the last tile of the sequence is the outgoing rank state
+        if (a.x_out != nullptr && w.t == a.tiles - 1 && row < D) {
+          float4* dst = reinterpret_cast<float4*>(a.x_out + (size_t)w.bh * D * E + (size_t)row * E + half * kHalfE);
+#pragma unroll
+          for (int q = 0; q < kHalfE / 4; ++q) dst[q] = make_float4(P[4 * q], P[4 * q + 1], P[4 * q + 2], P[4 * q + 3]);
+        }
+      }
+      if (tid == 64) TRACE(1 + i * 6 + 4);
+      // epilogue: OUT = O1 + lambda^row O2, staged in Y's buffer (the L MMA has read the scaled rows)
+      wait_or_fault(&o_full[p], ph, &dead, fault, kFaultMmaWait);
+      tc_fence_after_sync();
+      const float qd = decay_pow(sl2, row);
+#pragma unroll
+      for (int cc = 0; cc < WZ / 64; ++cc) {
+        const int col0 = half * (WZ / 2) + cc * 32;
+        stage_row32(t_s[p] + lane_base + col0, t_o2 + lane_base + col0, qd, sy[p], row, col0);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&t_free[p]);
+      mbar_arrive(&o2_free);
+      fence_async_smem();
+      mbar_arrive(&staged[p]);
+      if (tid == 64) TRACE(1 + i * 6 + 5);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 64) TRACE(63);
+  if (warp == 2) tmem_dealloc(tmem, 512);
+  if constexpr (FUSED) {
+    // the last CTA to finish advances the launch counter: the flags of this launch are stale from then on
+    if (tid == 0 && a.nspans > 1) {
+      __threadfence();
+      if (atomicAdd(a.sync + 1, 1u) == gridDim.x - 1) {
+        st_volatile_u32(a.sync + 1, 0u);
+        __threadfence();
+        st_volatile_u32(a.sync, step_s);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// walk, last to first tile, with the suffix state Dn (d x e) on chip:
+//   dK = dS_m^T Q + diag(lambda^(len-c)) V Dn^T
+//   dV = S_m^T dO + diag(lambda^(len-c)) K Dn
+//   Dn <- lambda^len Dn + Q^T diag(lambda^r) dO          (len = tokens in the tile, 128 but for a ragged tail)
+//
+// Shared memory: Q, dO (single buffers), K, V (double buffered), the state operand: seven 32 KB buffers.
+//   K: tile -> (after phase A) S_m -> (after phase B) staging tile of dK
+//   V: tile -> (after phase A) dS_m -> (after phase B) staging tile of dV
+//   Q: tile -> (after phase B) rows scaled in place for the state update
+// Tensor memory: T_S (S, then S_m^T dO), T_dS (dS, then the state update L), T_dK (V Dn^T, scaled by
+// rows, += dS_m^T Q), T_X (K Dn).
+// ---------------------------------------------------------------------------
+template <int D, int E>
+__global__ void __launch_bounds__(320, 1) k_walk_dkv(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+    const __grid_constant__ CUtensorMap map_dk, const __grid_constant__ CUtensorMap map_dv,
+    const float* __restrict__ s, const float* __restrict__ dn0, int h, int n, int tiles, int span, int nspans,
+    int items, int32_t* fault) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* sq = smem;
+  uint8_t* sdo = smem + kBuf;
+  uint8_t* sk[2] = {smem + 2 * kBuf, smem + 3 * kBuf};
+  uint8_t* sv[2] = {smem + 4 * kBuf, smem + 5 * kBuf};
+  uint8_t* sdn = smem + 6 * kBuf;
+  __shared__ uint64_t kv_full[2], staged[2];
+  __shared__ uint64_t qdo_full, dn_ready, a_done, sm_ready, b_done, qs_ready, l_done, e_free, l_free;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int dead;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    dead = 0;
+    for (int p = 0; p < 2; ++p) {
+      mbar_init(&kv_full[p], 1);
+      mbar_init(&staged[p], kWorkers);
+    }
+    mbar_init(&qdo_full, 1);
+    mbar_init(&dn_ready, kWorkers);
+    mbar_init(&a_done, 1);
+    mbar_init(&sm_ready, kWorkers);
+    mbar_init(&b_done, 1);
+    mbar_init(&qs_ready, kWorkers);
+    mbar_init(&l_done, 1);
+    mbar_init(&e_free, kWorkers);
+    mbar_init(&l_free, kWorkers);
+    fence_mbar_init();
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+    prefetch_tensormap(&map_do);
+    prefetch_tensormap(&map_dk);
+    prefetch_tensormap(&map_dv);
+  }
+  if (warp == 2) tmem_alloc(&tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t t_s = tmem, t_ds = tmem + 128, t_dk = tmem + 256, t_x = tmem + 384;
+  TileWalk w{items, nspans, span, tiles, 0, true};
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int i = 0;
+      int out_row[2] = {0, 0}, out_bh[2] = {0, 0};
+      for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++i) {
+        const int p = i & 1, u = i >> 1;
+        if (i >= 2) {
+          // dK and dV of tile i-2 are staged in this parity's K and V buffers
+          wait_or_fault(&staged[p], (u - 1) & 1, &dead, fault, kFaultMmaWait);
+          tma_store_4d(&map_dk, sk[p], 0, out_row[p], 0, out_bh[p]);
+          tma_store_4d(&map_dv, sv[p], 0, out_row[p], 0, out_bh[p]);
+          bulk_commit();
+          bulk_wait_read<0>();
+        }
+        mbar_expect_tx(&kv_full[p], C * (D + E) * 2);
+        tma_load_4d(sk[p], &map_k, &kv_full[p], 0, w.t * C, 0, w.bh);
+        tma_load_4d(sv[p], &map_v, &kv_full[p], 0, w.t * C, 0, w.bh);
+        if (i >= 1) wait_or_fault(&l_done, (i - 1) & 1, &dead, fault, kFaultMmaWait);  // Q, dO of tile i-1 are read
+        mbar_expect_tx(&qdo_full, C * (D + E) * 2);
+        tma_load_4d(sq, &map_q, &qdo_full, 0, w.t * C, 0, w.bh);
+        tma_load_4d(sdo, &map_do, &qdo_full, 0, w.t * C, 0, w.bh);
+        out_row[p] = w.t * C;
+        out_bh[p] = w.bh;
+      }
+      for (int j = (i >= 2 ? i - 2 : 0); j < i; ++j) {   // the last two tiles
+        const int p = j & 1, u = j >> 1;
+        wait_or_fault(&staged[p], u & 1, &dead, fault, kFaultMmaWait);
+        tma_store_4d(&map_dk, sk[p], 0, out_row[p], 0, out_bh[p]);
+        tma_store_4d(&map_dv, sv[p], 0, out_row[p], 0, out_bh[p]);
+        bulk_commit();
+      }
+      bulk_wait_all<0>();
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int i = 0;
+      for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++i) {
+        const int p = i & 1, ph = (i >> 1) & 1, one = i & 1;
+        wait_or_fault(&kv_full[p], ph, &dead, fault, kFaultTmaWait);
+        wait_or_fault(&dn_ready, one, &dead, fault, kFaultMmaWait);
+        if (i >= 1) {
+          wait_or_fault(&e_free, one ^ 1, &dead, fault, kFaultMmaWait);  // T_S, T_dK, T_X of tile i-1 are drained
+          wait_or_fault(&l_free, one ^ 1, &dead, fault, kFaultMmaWait);  // T_dS of tile i-1 is drained
+        }
+        tc_fence_after_sync();
+        // the state tile as [N = d rows] x [K = e columns] (V Dn^T) and as [K = d rows] x [N = e columns] (K Dn)
+        umma_gemm(t_dk, Operand{smem_u32(sv[p]), C, false}, Operand{smem_u32(sdn), D, false}, D, E / 16, false);
+        umma_gemm(t_x, Operand{smem_u32(sk[p]), C, false}, Operand{smem_u32(sdn), D, true}, E, D / 16, false);
+        wait_or_fault(&qdo_full, one, &dead, fault, kFaultTmaWait);
+        tc_fence_after_sync();
+        umma_gemm(t_s, Operand{smem_u32(sq), C, false}, Operand{smem_u32(sk[p]), C, false}, C, D / 16, false);
+        umma_gemm(t_ds, Operand{smem_u32(sdo), C, false}, Operand{smem_u32(sv[p]), C, false}, C, E / 16, false);
+        umma_commit(&a_done);
+        wait_or_fault(&sm_ready, one, &dead, fault, kFaultMmaWait);
+        tc_fence_after_sync();
+        umma_gemm(t_dk, Operand{smem_u32(sv[p]), C, true}, Operand{smem_u32(sq), C, true}, D, C / 16, true);   // += dS_m^T Q
+        umma_gemm(t_s, Operand{smem_u32(sk[p]), C, true}, Operand{smem_u32(sdo), C, true}, E, C / 16, false);   // S_m^T dO
+        umma_commit(&b_done);
+        wait_or_fault(&qs_ready, one, &dead, fault, kFaultMmaWait);
+        tc_fence_after_sync();
+        umma_gemm(t_ds, Operand{smem_u32(sq), C, true}, Operand{smem_u32(sdo), C, true}, E, C / 16, false);     // Q_s^T dO
+        umma_commit(&l_done);
+      }
+    }
+  } else {
+    const int cw = warp - 2;
+    const int row = (warp & 3) * 32 + lane;
+    const int half = cw >> 2;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    constexpr int kHalfE = E / 2;
+    float Dn[kHalfE];  // this thread's part of the suffix state: row `row`, columns [half * E/2, (half+1) * E/2)
+    int i = 0;
+    for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++i) {
+      const int p = i & 1, one = i & 1;
+      const float sl2 = s[w.bh % h] * kLog2e;
+      const float lam = exp2f(-sl2);
+      const int len = min(C, n - w.t * C);
+      if (w.first_of_item()) {
+        if (row < D) {
+          const float4* src = reinterpret_cast<const float4*>(dn0 + ((size_t)w.it * D + row) * E + half * kHalfE);
+#pragma unroll
+          for (int j = 0; j < kHalfE / 4; ++j) {
+            const float4 v = src[j];
+            Dn[4 * j] = v.x, Dn[4 * j + 1] = v.y, Dn[4 * j + 2] = v.z, Dn[4 * j + 3] = v.w;
+          }
+#pragma unroll
+          for (int j = 0; j < kHalfE; j += 8)
+            *reinterpret_cast<uint4*>(sdn + tile_offset(row, half * kHalfE + j, D)) =
+                make_uint4(pack_bf16(Dn[j], Dn[j + 1]), pack_bf16(Dn[j + 2], Dn[j + 3]),
+                           pack_bf16(Dn[j + 4], Dn[j + 5]), pack_bf16(Dn[j + 6], Dn[j + 7]));
+        }
+        fence_async_smem();
+        mbar_arrive(&dn_ready);
+      }
+      wait_or_fault(&a_done, one, &dead, fault, kFaultMmaWait);
+      tc_fence_after_sync();
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int col0 = half * 64 + cc * 32;
+        masked_store32(t_s + lane_base + col0, sk[p], row, col0, sl2, lam);    // S_m over the K tile
+        masked_store32(t_ds + lane_base + col0, sv[p], row, col0, sl2, lam);   // dS_m over the V tile
+      }
+      const float kd = decay_pow(sl2, max(len - row, 0));
+#pragma unroll
+      for (int cc = 0; cc < D / 64; ++cc) scale_tmem32(t_dk + lane_base + half * (D / 2) + cc * 32, kd);
+      tmem_st_wait();
+      fence_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&sm_ready);
+      wait_or_fault(&b_done, one, &dead, fault, kFaultMmaWait);
+      wait_or_fault(&qdo_full, one, &dead, fault, kFaultTmaWait);  // completed long ago: makes Q's bytes visible here
+      tc_fence_after_sync();
+      scale_row_pieces<D / 16>(sq, row, half * (D / 16), decay_pow(sl2, row), lane);
+      fence_async_smem();
+      mbar_arrive(&qs_ready);
+      // epilogue: dK and dV staged over S_m and dS_m (both read by the phase-B MMAs)
+#pragma unroll
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int col0 = half * (D / 2) + cc * 32;
+        stage_row32(t_dk + lane_base + col0, kNoAcc, 0.f, sk[p], row, col0);
+      }
+#pragma unroll
+      for (int cc = 0; cc < E / 64; ++cc) {
+        const int col0 = half * (E / 2) + cc * 32;
+        stage_row32(t_s + lane_base + col0, t_x + lane_base + col0, kd, sv[p], row, col0);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&e_free);
+      fence_async_smem();
+      mbar_arrive(&staged[p]);
+      wait_or_fault(&l_done, one, &dead, fault, kFaultMmaWait);
+      tc_fence_after_sync();
+      if (row < D) {
+        const float lam_len = decay_pow(sl2, len);
+#pragma unroll
+        for (int c0 = 0; c0 < kHalfE; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(t_ds + lane_base + half * kHalfE + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) Dn[c0 + j] = fmaf(lam_len, Dn[c0 + j], __uint_as_float(r[j]));
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&l_free);
+      if (!w.last_of_item()) {
+        if (row < D) {
+#pragma unroll
+          for (int j = 0; j < kHalfE; j += 8)
+            *reinterpret_cast<uint4*>(sdn + tile_offset(row, half * kHalfE + j, D)) =
+                make_uint4(pack_bf16(Dn[j], Dn[j + 1]), pack_bf16(Dn[j + 2], Dn[j + 3]),
+                           pack_bf16(Dn[j + 4], Dn[j + 5]), pack_bf16(Dn[j + 6], Dn[j + 7]));
+        }
+        fence_async_smem();
+        mbar_arrive(&dn_ready);
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+template <typename F>
+cudaError_t opt_in_smem(F* fn, size_t bytes) {
+  cudaError_t err = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (err != cudaSuccess) g_failed_step = "cudaFuncSetAttribute(max dynamic shared memory)";
+  return err;
+}
+
+cudaError_t seq_map(CUtensorMap* map, const void* base, const Dims& m, int width, const char* what) {
+  cudaError_t err = make_seq_tile_map(map, base, (uint64_t)m.b * m.h, (uint64_t)m.n, (uint32_t)width, C);
+  if (err != cudaSuccess) {
+    static thread_local char text[160];
+    snprintf(text, sizeof(text), "tensor map (%s): CUresult %d, base %p, b*h %d, n %d, width %d", what,
+             last_encode_result(), base, m.b * m.h, m.n, width);
+    g_failed_step = text;
+  }
+  return err;
+}
+
+cudaError_t launched(const char* what) {
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) g_failed_step = what;
+  return err;
+}
+
+int grid_for(int items) {
+  const int sms = sm_count();
+  return items < sms ? items : sms;
+}
+
+template <int D, int E>
+cudaError_t launch_span_totals(const Dims& m, const void* a, const void* bten, const float* s, float* totals,
+                               bool reverse, cudaStream_t st) {
+  CUtensorMap ma, mb;
+  cudaError_t err;
+  if ((err = seq_map(&ma, a, m, D, "span totals, first operand")) != cudaSuccess) return err;
+  if ((err = seq_map(&mb, bten, m, E, "span totals, second operand")) != cudaSuccess) return err;
+  int32_t* fault = nullptr;
+  if ((err = fault_word_address(&fault)) != cudaSuccess) return err;
+  const size_t smem = (size_t)3 * C * (D + E) * 2 + 1024;
+  if ((err = opt_in_smem(k_span_totals<D, E>, smem)) != cudaSuccess) return err;
+  const int items = m.b * m.h * m.nc;
+  k_span_totals<D, E><<<grid_for(items), 320, smem, st>>>(ma, mb, s, totals, m.h, m.n, m.tiles, m.span, m.nc, items,
+                                                          reverse ? 1 : 0, fault);
+  return launched("launch of the span-total kernel");
+}
+
+// a launch whose CTAs wait for one another: all of them must be resident
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, size_t smem, cudaStream_t st, bool cooperative,
+                          Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(320);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = cooperative ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+constexpr long long kFlagWaitClocks = 1000000000LL;   // about half a second
+
+template <int D, int E, bool DQ, bool FUSED>
+cudaError_t launch_walk_out(const Dims& m, const void* x, const void* y, const void* z, void* out, WalkArgs a,
+                            cudaStream_t st) {
+  constexpr int WX = DQ ? E : D, WZ = DQ ? D : E;
+  CUtensorMap mx, my, mz, mo;
+  cudaError_t err;
+  if ((err = seq_map(&mx, x, m, WX, DQ ? "do" : "q")) != cudaSuccess) return err;
+  if ((err = seq_map(&my, y, m, WX, DQ ? "v" : "k")) != cudaSuccess) return err;
+  if ((err = seq_map(&mz, z, m, WZ, DQ ? "k" : "v")) != cudaSuccess) return err;
+  if ((err = seq_map(&mo, out, m, WZ, DQ ? "dq" : "o")) != cudaSuccess) return err;
+  if ((err = fault_word_address(&a.fault)) != cudaSuccess) return err;
+  const size_t smem = (size_t)7 * kBuf + 1024;
+  if ((err = opt_in_smem(k_walk_out<D, E, DQ, FUSED>, smem)) != cudaSuccess) return err;
+  a.h = m.h, a.n = m.n, a.tiles = m.tiles, a.span = m.span, a.nspans = m.nc, a.items = m.b * m.h * m.nc;
+  a.wait_clocks = kFlagWaitClocks;
+  const bool waits = FUSED && m.nc > 1;   // CTAs wait for one another: one span each, all resident
+  if (waits && a.items > sm_count()) {
+    g_failed_step = "fused walk kernel: more spans than SMs";
+    return cudaErrorInvalidConfiguration;
+  }
+  if ((err = launch_kernel(k_walk_out<D, E, DQ, FUSED>, grid_for(a.items), smem, st, waits, mx, my, mz, mo, a)) !=
+      cudaSuccess) {
+    g_failed_step = "launch of a walk kernel";
+    return err;
+  }
+  return launched(DQ ? "launch of the dq walk kernel" : "launch of the forward walk kernel");
+}
+
+template <int D, int E>
+cudaError_t launch_walk_dkv(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
+                            const float* s, const float* dn0, void* dk, void* dv, cudaStream_t st) {
+  CUtensorMap mq, mk, mv, mdo, mdk, mdv;
+  cudaError_t err;
+  if ((err = seq_map(&mq, q, m, D, "q")) != cudaSuccess) return err;
+  if ((err = seq_map(&mk, k, m, D, "k")) != cudaSuccess) return err;
+  if ((err = seq_map(&mv, v, m, E, "v")) != cudaSuccess) return err;
+  if ((err = seq_map(&mdo, d_o, m, E, "do")) != cudaSuccess) return err;
+  if ((err = seq_map(&mdk, dk, m, D, "dk")) != cudaSuccess) return err;
+  if ((err = seq_map(&mdv, dv, m, E, "dv")) != cudaSuccess) return err;
+  int32_t* fault = nullptr;
+  if ((err = fault_word_address(&fault)) != cudaSuccess) return err;
+  const size_t smem = (size_t)7 * kBuf + 1024;
+  if ((err = opt_in_smem(k_walk_dkv<D, E>, smem)) != cudaSuccess) return err;
+  const int items = m.b * m.h * m.nc;
+  k_walk_dkv<D, E><<<grid_for(items), 320, smem, st>>>(mq, mk, mv, mdo, mdk, mdv, s, dn0, m.h, m.n, m.tiles, m.span,
+                                                       m.nc, items, fault);
+  return launched("launch of the dk/dv walk kernel");
+}
+
+}  // namespace
+
+#define LASP_DISPATCH_DE(m, CALL)                                        \
+  do {                                                                    \
+    if ((m).d == 128 && (m).e == 128) return CALL(128, 128);              \
+    if ((m).d == 128 && (m).e == 64) return CALL(128, 64);                \
+    if ((m).d == 64 && (m).e == 128) return CALL(64, 128);                \
+    if ((m).d == 64 && (m).e == 64) return CALL(64, 64);                  \
+    return cudaErrorInvalidValue;                                         \
+  } while (0)
+
+cudaError_t walk_span_totals(const Dims& m, const void* a, const void* bten, const float* s, float* totals,
+                             bool reverse, cudaStream_t st) {
+#define LASP_CALL(DD, EE) launch_span_totals<DD, EE>(m, a, bten, s, totals, reverse, st)
+  LASP_DISPATCH_DE(m, LASP_CALL);
+#undef LASP_CALL
+}
+
+cudaError_t walk_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
+                            const float* prefix, void* o, cudaStream_t st) {
+  WalkArgs a = {};
+  a.s = s, a.p0 = prefix;
+#define LASP_CALL(DD, EE) launch_walk_out<DD, EE, false, false>(m, q, k, v, o, a, st)
+  LASP_DISPATCH_DE(m, LASP_CALL);
+#undef LASP_CALL
+}
+
+cudaError_t walk_fwd_fused(const Dims& m, const void* q, const void* k, const void* v, const float* s,
+                           const float* x_in, float* x_out, uint32_t* sync, float* totals, float* prefix, void* o,
+                           cudaStream_t st) {
+  WalkArgs a = {};
+  a.s = s, a.x_in = x_in, a.x_out = x_out, a.sync = sync, a.totals = totals, a.p0_save = prefix;
+#define LASP_CALL(DD, EE) launch_walk_out<DD, EE, false, true>(m, q, k, v, o, a, st)
+  LASP_DISPATCH_DE(m, LASP_CALL);
+#undef LASP_CALL
+}
+
+cudaError_t walk_bwd_dq(const Dims& m, const void* k, const void* v, const void* d_o, const float* s,
+                        const float* prefix, void* dq, cudaStream_t st) {
+  WalkArgs a = {};
+  a.s = s, a.p0 = prefix;
+#define LASP_CALL(DD, EE) launch_walk_out<DD, EE, true, false>(m, d_o, v, k, dq, a, st)
+  LASP_DISPATCH_DE(m, LASP_CALL);
+#undef LASP_CALL
+}
+
+cudaError_t walk_bwd_dkv(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
+                         const float* s, const float* suffix, void* dk, void* dv, cudaStream_t st) {
+#define LASP_CALL(DD, EE) launch_walk_dkv<DD, EE>(m, q, k, v, d_o, s, suffix, dk, dv, st)
+  LASP_DISPATCH_DE(m, LASP_CALL);
+#undef LASP_CALL
+}
+
+#ifdef LASP_TRACE
+extern "C" __attribute__((visibility("default"))) int lasp_b200_debug_trace(long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * 160 * 64);
+}
+#endif
+
+}  // namespace lasp

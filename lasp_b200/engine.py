@@ -110,8 +110,16 @@ def make_plan(b: int, h: int, n: int, d: int, e: int, dtype: torch.dtype, path: 
     return Plan(prob, b, h, n, d, e, resolved, chunk, ws)
 
 
+SYNC_BYTES = 4096
+
+
 def new_workspace(plan: Plan, device) -> torch.Tensor:
-    return torch.empty(plan.ws_bytes, dtype=torch.uint8, device=device)
+    """Workspace of a forward or backward call.  Its first 4 KB hold the words through which the CTAs of
+    the fused kernels synchronise: they must be zero before the workspace is first used (the library keeps
+    them consistent afterwards)."""
+    ws = torch.empty(plan.ws_bytes, dtype=torch.uint8, device=device)
+    ws[:SYNC_BYTES].zero_()
+    return ws
 
 
 def _slopes(s: torch.Tensor, h: int, device) -> torch.Tensor:
