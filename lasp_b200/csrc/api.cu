@@ -333,6 +333,15 @@ int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stre
   int st = check_bwd(p, a, &m, true);
   if (st != LASP_OK) return st;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (fusable(m)) {
+    // dQ walks forward over the border states the forward pass kept; dK, dV walk backward in one fused launch
+    if ((st = cuda_fail(lasp::walk_bwd_dq(m, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m), a->dq,
+                                          cs))) != LASP_OK)
+      return st;
+    return cuda_fail(lasp::walk_bwd_dkv_fused(m, a->q, a->k, a->v, a->d_o, a->s, a->dkv_in, a->dkv_out,
+                                              lasp::ws_walk_sync(a->ws), lasp::ws_walk_totals(a->ws), a->dk, a->dv,
+                                              cs));
+  }
   const bool chained = chain_launches() && m.path == LASP_PATH_TENSOR;
   if ((st = bwd_chunk_states(m, a, cs, chained)) != LASP_OK) return st;
   if ((st = bwd_scan(m, a, cs, chained)) != LASP_OK) return st;

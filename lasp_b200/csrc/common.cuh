@@ -43,6 +43,14 @@ int sm_count();
 
 inline size_t state_elems(const Dims& m) { return (size_t)m.b * m.h * m.nc * m.d * m.e; }
 
+// Span states of the walk kernels are kept in global memory in "lane order": the float4 holding
+// columns 4g..4g+3 of row r of a d x e state sits at float4 index g*d + r, so that the 32 rows a warp
+// owns are contiguous for each of its accesses.  Rank states handed in and out by the caller stay
+// row-major; `rows` > 0 on the elementwise kernels below selects the conversion (0 = plain row-major).
+__host__ __device__ inline int lane_order_to_row_major(int f4, int rows, int cols) {
+  const int g = f4 / rows, r = f4 - g * rows;
+  return r * (cols / 4) + g;
+}
 constexpr size_t kWalkSyncBytes = 4096;
 inline uint32_t* ws_walk_sync(void* ws) { return reinterpret_cast<uint32_t*>(ws); }
 inline float* ws_walk_totals(void* ws) { return reinterpret_cast<float*>(static_cast<char*>(ws) + kWalkSyncBytes); }
@@ -125,5 +133,8 @@ cudaError_t walk_bwd_dq(const Dims& m, const void* k, const void* v, const void*
                         const float* prefix, void* dq, cudaStream_t st);
 cudaError_t walk_bwd_dkv(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
                          const float* s, const float* suffix, void* dk, void* dv, cudaStream_t st);
+cudaError_t walk_bwd_dkv_fused(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
+                               const float* s, const float* x_in, float* x_out, uint32_t* sync, float* totals,
+                               void* dk, void* dv, cudaStream_t st);
 
 }  // namespace lasp

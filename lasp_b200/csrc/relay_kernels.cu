@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(256) k_state_exchange(const ExchangeParams p) 
 template <typename T>
 __global__ void __launch_bounds__(128) k_state_total(const float* __restrict__ s, const T* __restrict__ local,
                                                      float* __restrict__ total, int h, int n, int de, int nc,
-                                                     int chunk, int reverse) {
+                                                     int chunk, int reverse, int lane_rows, int cols) {
   const int bh = blockIdx.y;
   const int el = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (el >= de) return;
@@ -217,7 +217,8 @@ __global__ void __launch_bounds__(128) k_state_total(const float* __restrict__ s
       }
     }
   }
-  *reinterpret_cast<float4*>(total + (size_t)bh * de + el) = p;
+  const int ext = lane_rows > 0 ? lane_order_to_row_major(el / 4, lane_rows, cols) * 4 : el;
+  *reinterpret_cast<float4*>(total + (size_t)bh * de + ext) = p;
 }
 
 }  // namespace
@@ -228,10 +229,11 @@ cudaError_t state_total(const Dims& m, const float* s, const void* local, float*
   dim3 grid((de / 4 + 127) / 128, m.b * m.h);
   if (m.path == LASP_PATH_TENSOR && !m.walk)
     k_state_total<__nv_bfloat16><<<grid, 128, 0, st>>>(s, static_cast<const __nv_bfloat16*>(local), total, m.h, m.n,
-                                                        de, m.nc, m.chunk, reverse ? 1 : 0);
+                                                        de, m.nc, m.chunk, reverse ? 1 : 0, 0, m.e);
   else
     k_state_total<float><<<grid, 128, 0, st>>>(s, m.walk ? ws_walk_border(local, m) : static_cast<const float*>(local),
-                                               total, m.h, m.n, de, m.nc, m.chunk, reverse ? 1 : 0);
+                                               total, m.h, m.n, de, m.nc, m.chunk, reverse ? 1 : 0, m.walk ? m.d : 0,
+                                               m.e);
   return cudaGetLastError();
 }
 

@@ -148,16 +148,19 @@ __global__ void __launch_bounds__(256) k_scan_bf16(const float* __restrict__ s,
 
 __global__ void __launch_bounds__(256) k_scan(const float* __restrict__ s, float* __restrict__ states,
                                               const float* __restrict__ x_in, float* __restrict__ x_out, int h,
-                                              int n, int de, int nc, int chunk, int reverse) {
+                                              int n, int de, int nc, int chunk, int reverse, int lane_rows,
+                                              int cols) {
   const int bh = blockIdx.y;
   const int el = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (el >= de) return;
+  // where this float4 lives in the caller's row-major rank states
+  const int ext = lane_rows > 0 ? lane_order_to_row_major(el / 4, lane_rows, cols) * 4 : el;
   const float sh = s[bh % h];
   const float full = expf(-sh * (float)chunk);
   const int last_len = n - (nc - 1) * chunk;
   const float tail = expf(-sh * (float)last_len);
   float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (x_in) p = *reinterpret_cast<const float4*>(x_in + (size_t)bh * de + el);
+  if (x_in) p = *reinterpret_cast<const float4*>(x_in + (size_t)bh * de + ext);
   float* base = states + (size_t)bh * nc * de + el;
   for (int i0 = 0; i0 < nc; i0 += kScanBatch) {
     float4 loc[kScanBatch];
@@ -180,7 +183,7 @@ __global__ void __launch_bounds__(256) k_scan(const float* __restrict__ s, float
       }
     }
   }
-  if (x_out) *reinterpret_cast<float4*>(x_out + (size_t)bh * de + el) = p;
+  if (x_out) *reinterpret_cast<float4*>(x_out + (size_t)bh * de + ext) = p;
 }
 
 __global__ void __launch_bounds__(256) k_state_combine(const float* __restrict__ s, const float* __restrict__ x_in,
@@ -479,7 +482,8 @@ cudaError_t scan_states(const Dims& m, const float* s, float* states, const floa
                         cudaStream_t st) {
   const int de = m.d * m.e;
   dim3 grid((de / 4 + 255) / 256, m.b * m.h);
-  k_scan<<<grid, 256, 0, st>>>(s, states, x_in, x_out, m.h, m.n, de, m.nc, m.chunk, reverse ? 1 : 0);
+  k_scan<<<grid, 256, 0, st>>>(s, states, x_in, x_out, m.h, m.n, de, m.nc, m.chunk, reverse ? 1 : 0, m.walk ? m.d : 0,
+                               m.e);
   return cudaGetLastError();
 }
 

@@ -180,6 +180,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// 32 lanes x 16 consecutive 32-bit columns
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------
@@ -211,6 +220,17 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t 
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with the A operand in tensor memory: lane = row of A, and each 32-bit column holds two
+// consecutive K elements (bf16), so one instruction (16 K elements) reads 8 columns from a_tmem on.
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // the mbarrier gets one arrival when every MMA issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -239,6 +259,18 @@ __device__ __forceinline__ void umma_gemm(uint32_t d_tmem, const Operand& a, con
   const uint32_t idesc = umma_idesc(128, n, a.mn_major, b.mn_major);
   for (uint32_t ks = 0; ks < ksteps; ++ks)
     umma(d_tmem, operand_desc(a, ks), operand_desc(b, ks), idesc, (accumulate || ks > 0) ? 1u : 0u);
+}
+
+// D[128 x n] (+)= A x B over 8 k-steps with A = a 128 x 128 bf16 matrix in tensor memory.  `split`:
+// K elements 0..63 sit in columns [0, 32) and 64..127 in columns [64, 96) of the region at a_tmem (what
+// packing an fp32 accumulator in place, half by half, leaves); otherwise in columns [0, 64).
+__device__ __forceinline__ void umma_gemm_ts(uint32_t d_tmem, uint32_t a_tmem, bool split, const Operand& b,
+                                             uint32_t n, bool accumulate) {
+  const uint32_t idesc = umma_idesc(128, n, false, b.mn_major);
+  for (uint32_t ks = 0; ks < 8; ++ks) {
+    const uint32_t col = split ? (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8) : ks * 8;
+    umma_ts(d_tmem, a_tmem + col, operand_desc(b, ks), idesc, (accumulate || ks > 0) ? 1u : 0u);
+  }
 }
 
 // ---------------------------------------------------------------------------

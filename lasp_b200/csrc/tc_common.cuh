@@ -120,6 +120,47 @@ __device__ __forceinline__ void masked_store32(uint32_t taddr, uint8_t* tile, in
   }
 }
 
+// The same mask, but the result stays in tensor memory as the A operand of the next MMA: 32 fp32
+// columns at `src` (columns col0 .. col0+31 of the score tile) become 16 columns of bf16 pairs at `dst`.
+// TRANSPOSED = false: lane = query row r, column = key c:  [r >= c] lambda^(r-c)
+// TRANSPOSED = true : lane = key c, column = query row r:  [r >= c] lambda^(r-c)   (the tile is S^T)
+template <bool TRANSPOSED>
+__device__ __forceinline__ void masked_pack32(uint32_t src, int row, int col0, float sl2, float lam,
+                                              uint32_t (&out)[16]) {
+  const int row0 = row & ~31;
+  const bool none = TRANSPOSED ? (col0 + 31 < row0) : (col0 > row0 + 31);   // same for every lane of the warp
+  if (none) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) out[j] = 0u;
+    return;
+  }
+  uint32_t r[32];
+  tmem_ld32(src, r);
+  float f[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    // the chain of a group of eight columns starts at its live column nearest the diagonal
+    const int start = TRANSPOSED ? max(row, col0 + 8 * g) : min(row, col0 + 8 * g + 7);
+    f[g] = decay_pow(sl2, TRANSPOSED ? start - row : row - start);
+  }
+  tmem_ld_wait();
+  const bool all = TRANSPOSED ? (col0 >= row0 + 31) : (col0 + 31 <= row0);
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float m[8];
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+      const int j = TRANSPOSED ? jj : 7 - jj;           // away from the diagonal
+      const int col = col0 + 8 * g + j;
+      const bool live = all || (TRANSPOSED ? col >= row : col <= row);
+      m[j] = live ? __uint_as_float(r[8 * g + j]) * f[g] : 0.f;
+      f[g] = live ? f[g] * lam : f[g];
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) out[4 * g + j] = pack_bf16(m[2 * j], m[2 * j + 1]);
+  }
+}
+
 // Multiplies CHUNKS 16-byte pieces of row `row` of a swizzled tile of C rows by w, in place, starting
 // at piece `first` (pieces are counted slab by slab; a row keeps its pieces under the swizzle, so the
 // physical position inside the row does not matter).  `lane` rotates the order to spread the banks.

@@ -31,12 +31,55 @@ using namespace tc;
 #ifdef LASP_TRACE
 __device__ long long g_trace[160 * 64];
 #define TRACE(slot) do { if (blockIdx.x < 160 && (slot) < 64) g_trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
+__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define GTRACE(slot) do { if (blockIdx.x < 160) g_trace[blockIdx.x * 64 + (slot)] = gtime(); } while (0)
 #else
 #define TRACE(slot) do {} while (0)
+#define GTRACE(slot) do {} while (0)
 #endif
 
 constexpr int kBuf = 32768;       // one shared-memory buffer: a 128 x 128 bf16 tile
 constexpr int kWorkers = 256;     // warps 2..9
+
+// Global-memory image of a d x e span state in lane order (see common.cuh): this thread's part is row
+// `row`, columns [col0, col0 + N).
+template <int N, int ROWS, bool COHERENT>
+__device__ __forceinline__ void load_state(const float* state, int row, int col0, float (&P)[N]) {
+  const float4* src = reinterpret_cast<const float4*>(state) + (size_t)(col0 / 4) * ROWS + row;
+#pragma unroll
+  for (int q = 0; q < N / 4; ++q) {
+    const float4 v = COHERENT ? __ldcg(src + (size_t)q * ROWS) : src[(size_t)q * ROWS];
+    P[4 * q] = v.x, P[4 * q + 1] = v.y, P[4 * q + 2] = v.z, P[4 * q + 3] = v.w;
+  }
+}
+template <int N, int ROWS>
+__device__ __forceinline__ void fma_state(const float* state, int row, int col0, float dec, float (&P)[N]) {
+  const float4* src = reinterpret_cast<const float4*>(state) + (size_t)(col0 / 4) * ROWS + row;
+  float4 v[N / 4];
+#pragma unroll
+  for (int q = 0; q < N / 4; ++q) v[q] = __ldcg(src + (size_t)q * ROWS);   // written by another CTA of this launch
+#pragma unroll
+  for (int q = 0; q < N / 4; ++q) {
+    P[4 * q] = fmaf(dec, v[q].x, P[4 * q]), P[4 * q + 1] = fmaf(dec, v[q].y, P[4 * q + 1]);
+    P[4 * q + 2] = fmaf(dec, v[q].z, P[4 * q + 2]), P[4 * q + 3] = fmaf(dec, v[q].w, P[4 * q + 3]);
+  }
+}
+template <int N, int ROWS>
+__device__ __forceinline__ void store_state(float* state, int row, int col0, const float (&P)[N]) {
+  float4* dst = reinterpret_cast<float4*>(state) + (size_t)(col0 / 4) * ROWS + row;
+#pragma unroll
+  for (int q = 0; q < N / 4; ++q) dst[(size_t)q * ROWS] = make_float4(P[4 * q], P[4 * q + 1], P[4 * q + 2], P[4 * q + 3]);
+}
+// 32 accumulator columns of this thread's row -> lane-order state
+template <int ROWS>
+__device__ __forceinline__ void store_state32(float* state, int row, int col0, const uint32_t (&r)[32]) {
+  float4* dst = reinterpret_cast<float4*>(state) + (size_t)(col0 / 4) * ROWS + row;
+#pragma unroll
+  for (int q = 0; q < 8; ++q)
+    dst[(size_t)q * ROWS] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                        __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+}
+
 
 // ---------------------------------------------------------------------------
 // span totals: totals[item][i][j] = sum_c w_c A[c][i] B[c][j] over the span's tokens
@@ -136,16 +179,12 @@ __global__ void __launch_bounds__(320, 1) k_span_totals(const __grid_constant__ 
       wait_or_fault(&acc_full[li & 1], (li >> 1) & 1, &dead, fault, kFaultMmaWait);
       tc_fence_after_sync();
       if (row < D) {
-        float* out = totals + ((size_t)w.it * D + row) * E;
 #pragma unroll
         for (int c0 = 0; c0 < E; c0 += 32) {
           uint32_t a[32];
           tmem_ld32(tmem + 128 * (li & 1) + lane_base + c0, a);
           tmem_ld_wait();
-#pragma unroll
-          for (int q = 0; q < 32; q += 4)
-            *reinterpret_cast<float4*>(out + c0 + q) = make_float4(__uint_as_float(a[q]), __uint_as_float(a[q + 1]),
-                                                                   __uint_as_float(a[q + 2]), __uint_as_float(a[q + 3]));
+          store_state32<D>(totals + (size_t)w.it * D * E, row, c0, a);
         }
       }
       tc_fence_before_sync();
@@ -212,10 +251,11 @@ __device__ __forceinline__ void write_state_operand(uint8_t* tile, int rows, int
 // half of the columns) and bf16 in shared memory as the operand of X op(P).
 //
 // Shared memory: X, Y, Z double buffered and the state operand, seven 32 KB buffers.  A buffer's life
-// inside a tile:  X: tile -> (after S, O2)  masked scores S_m -> free after O1
+// inside a tile:  X: tile -> free after S and O2
 //                 Y: tile -> (after S) rows scaled in place -> free after L -> staging tile of OUT
 //                 Z: tile -> free after L and O1
-// Tensor memory: S (two buffers; O1 = S_m Z is written over S), O2 = X op(P), L = the state update.
+// Tensor memory: S (two buffers; the masked scores are packed to bf16 over S itself and feed O1 as its A
+// operand from tensor memory), O (X op(P), rows scaled by lambda^r in place, += S_m Z), L = the state update.
 //   warp 0 (one lane)  producer: loads, and the TMA stores of the finished staging tiles
 //   warp 1 (one lane)  tensor-core issuer
 //   warps 2-9          mask, row scaling, state update, epilogue
@@ -236,6 +276,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
                                                      const __grid_constant__ CUtensorMap map_out,
                                                      const __grid_constant__ WalkArgs a) {
   static_assert(!(DQ && FUSED), "dQ walks over states the forward pass kept");
+  if (threadIdx.x == 0) GTRACE(56);
   constexpr int WX = DQ ? E : D;  // width of X and Y
   constexpr int WZ = DQ ? D : E;  // width of Z and OUT
   extern __shared__ uint8_t smem_raw[];
@@ -244,8 +285,8 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
   uint8_t* sy[2] = {smem + 2 * kBuf, smem + 3 * kBuf};
   uint8_t* sz[2] = {smem + 4 * kBuf, smem + 5 * kBuf};
   uint8_t* sp = smem + 6 * kBuf;
-  __shared__ uint64_t x_full[2], y_full[2], z_full[2], s_full[2], sm_ready[2], o_full[2], t_free[2], staged[2];
-  __shared__ uint64_t p_ready, l_free, o2_free, ys_ready, o2_full, l_full;
+  __shared__ uint64_t x_full[2], y_full[2], z_full[2], s_full[2], sm_ready[2], o_full[2], o2_full[2], staged[2];
+  __shared__ uint64_t p_ready, l_free, o_free, ys_ready, o2s_ready, l_full;
   __shared__ uint64_t ring_full[2], ring_scaled[2], ring_empty[2], sum_done;   // the span-total phase
   __shared__ uint32_t tmem_slot, step_s;
   __shared__ int dead;
@@ -260,7 +301,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       mbar_init(&s_full[p], 1);
       mbar_init(&sm_ready[p], kWorkers);
       mbar_init(&o_full[p], 1);
-      mbar_init(&t_free[p], kWorkers);
+      mbar_init(&o2_full[p], 1);
       mbar_init(&staged[p], kWorkers);
       mbar_init(&ring_full[p], 1);
       mbar_init(&ring_scaled[p], kWorkers);
@@ -268,9 +309,9 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
     }
     mbar_init(&p_ready, kWorkers);
     mbar_init(&l_free, kWorkers);
-    mbar_init(&o2_free, kWorkers);
+    mbar_init(&o_free, kWorkers);
     mbar_init(&ys_ready, kWorkers);
-    mbar_init(&o2_full, 1);
+    mbar_init(&o2s_ready, kWorkers);
     mbar_init(&l_full, 1);
     mbar_init(&sum_done, 1);
     fence_mbar_init();
@@ -286,7 +327,8 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
   if (tid == 64) TRACE(0);
-  const uint32_t t_s[2] = {tmem, tmem + 128}, t_o2 = tmem + 256, t_l = tmem + 384;
+  if (tid == 64) GTRACE(57);
+  const uint32_t t_s[2] = {tmem, tmem + 128}, t_o = tmem + 256, t_l = tmem + 384;
   TileWalk w{a.items, a.nspans, a.span, a.tiles, 0, false};
   // the span-total phase: only with several spans per sequence, and then this CTA has one span
   bool sums = false;
@@ -323,11 +365,12 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       int out_row[2] = {0, 0}, out_bh[2] = {0, 0};
       for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++i) {
         const int p = i & 1, u = i >> 1;
-        if (i >= 2) wait_or_fault(&o_full[p], (u - 1) & 1, &dead, fault, kFaultMmaWait);  // X, Z of tile i-2 are read
         if (i >= x_issued) {
+          if (i >= 2) wait_or_fault(&o2_full[p], (u - 1) & 1, &dead, fault, kFaultMmaWait);  // S, O2 of tile i-2 read X
           mbar_expect_tx(&x_full[p], C * WX * 2);
           tma_load_4d(sx[p], &map_x, &x_full[p], 0, w.t * C, 0, w.bh);
         }
+        if (i >= 2) wait_or_fault(&o_full[p], (u - 1) & 1, &dead, fault, kFaultMmaWait);     // L, O1 of tile i-2 read Z
         mbar_expect_tx(&z_full[p], C * WZ * 2);
         tma_load_4d(sz[p], &map_z, &z_full[p], 0, w.t * C, 0, w.bh);
         if (i >= 2) {
@@ -364,28 +407,31 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       }
       int total = 0;
       for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next()) ++total;
-      // Issue order: S of tile i+1 goes out before O1 of tile i, so that the score chain of the next
-      // tile (S -> mask) never waits for this tile's mask; the state chain (row scaling -> L -> update
-      // -> O2 of the next tile) is issued as soon as its inputs exist.
+      // Per tile: O2 = X op(P) as soon as the state operand exists; L once Y's rows are scaled; O1 = S_m Z
+      // (S_m read from tensor memory) on top of the row-scaled O2 once both are ready; and S of the next
+      // tile whenever its inputs are there, so that the next tile's mask never waits.
+      auto issue_s = [&](int j) {
+        const int q = j & 1;
+        tc_fence_after_sync();
+        umma_gemm(t_s[q], Operand{smem_u32(sx[q]), C, false}, Operand{smem_u32(sy[q]), C, false}, C, WX / 16, false);
+        umma_commit(&s_full[q]);
+      };
       if (total > 0) {
         wait_or_fault(&x_full[0], 0, &dead, fault, kFaultTmaWait);
         wait_or_fault(&y_full[0], 0, &dead, fault, kFaultTmaWait);
-        tc_fence_after_sync();
-        umma_gemm(t_s[0], Operand{smem_u32(sx[0]), C, false}, Operand{smem_u32(sy[0]), C, false}, C, WX / 16, false);
-        umma_commit(&s_full[0]);
+        issue_s(0);
       }
       for (int i = 0; i < total; ++i) {
         const int p = i & 1, ph = (i >> 1) & 1, one = i & 1;
-        // O2 = X op(P): needs this tile's state operand and the accumulator drained by the previous epilogue
         wait_or_fault(&p_ready, one, &dead, fault, kFaultMmaWait);
-        if (i >= 1) wait_or_fault(&o2_free, one ^ 1, &dead, fault, kFaultMmaWait);
+        if (i >= 1) wait_or_fault(&o_free, one ^ 1, &dead, fault, kFaultMmaWait);   // the epilogue has drained O
         TRACE(32 + i * 5 + 0);
         tc_fence_after_sync();
         if constexpr (!DQ)  // X P: the state tile as [K = d rows] x [N = e columns]
-          umma_gemm(t_o2, Operand{smem_u32(sx[p]), C, false}, Operand{smem_u32(sp), D, true}, E, D / 16, false);
+          umma_gemm(t_o, Operand{smem_u32(sx[p]), C, false}, Operand{smem_u32(sp), D, true}, E, D / 16, false);
         else                // X P^T: the state tile as [N = d rows] x [K = e columns]
-          umma_gemm(t_o2, Operand{smem_u32(sx[p]), C, false}, Operand{smem_u32(sp), D, false}, D, E / 16, false);
-        umma_commit(&o2_full);
+          umma_gemm(t_o, Operand{smem_u32(sx[p]), C, false}, Operand{smem_u32(sp), D, false}, D, E / 16, false);
+        umma_commit(&o2_full[p]);
         // L = K^T diag(w) V (d x e), the scaled rows being Y's
         wait_or_fault(&ys_ready, one, &dead, fault, kFaultMmaWait);
         wait_or_fault(&z_full[p], ph, &dead, fault, kFaultTmaWait);
@@ -397,31 +443,31 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
         else
           umma_gemm(t_l, Operand{smem_u32(sz[p]), C, true}, Operand{smem_u32(sy[p]), C, true}, E, C / 16, false);
         umma_commit(&l_full);
-        // S of the next tile goes out before O1 of this one when its inputs are already there (the usual
-        // case), so that the next tile's mask never waits; otherwise O1 first
+        // O1 and the next S, whichever is ready first (O1 preferred)
         const int q = (i + 1) & 1, uq = (i + 1) >> 1;
-        bool next_s = i + 1 < total;
-        if (next_s && mbar_test_wait(&x_full[q], uq & 1) && mbar_test_wait(&y_full[q], uq & 1) &&
-            (i + 1 < 2 || mbar_test_wait(&t_free[q], (uq - 1) & 1))) {
-          tc_fence_after_sync();
-          umma_gemm(t_s[q], Operand{smem_u32(sx[q]), C, false}, Operand{smem_u32(sy[q]), C, false}, C, WX / 16, false);
-          umma_commit(&s_full[q]);
-          next_s = false;
-        }
-        TRACE(32 + i * 5 + 2);
-        // O1 = S_m Z over S's columns
-        wait_or_fault(&sm_ready[p], ph, &dead, fault, kFaultMmaWait);
-        TRACE(32 + i * 5 + 3);
-        tc_fence_after_sync();
-        umma_gemm(t_s[p], Operand{smem_u32(sx[p]), C, false}, Operand{smem_u32(sz[p]), C, true}, WZ, C / 16, false);
-        umma_commit(&o_full[p]);
-        if (next_s) {
-          wait_or_fault(&x_full[q], uq & 1, &dead, fault, kFaultTmaWait);
-          wait_or_fault(&y_full[q], uq & 1, &dead, fault, kFaultTmaWait);
-          if (i + 1 >= 2) wait_or_fault(&t_free[q], (uq - 1) & 1, &dead, fault, kFaultMmaWait);
-          tc_fence_after_sync();
-          umma_gemm(t_s[q], Operand{smem_u32(sx[q]), C, false}, Operand{smem_u32(sy[q]), C, false}, C, WX / 16, false);
-          umma_commit(&s_full[q]);
+        bool need_o1 = true, need_s = i + 1 < total;
+        const long long t0 = clock64();
+        while ((need_o1 || need_s) && !dead) {
+          if (need_o1 && mbar_test_wait(&sm_ready[p], ph) && mbar_test_wait(&o2s_ready, one)) {
+            TRACE(32 + i * 5 + 3);
+            tc_fence_after_sync();
+            umma_gemm_ts(t_o, t_s[p], true, Operand{smem_u32(sz[p]), C, true}, WZ, true);
+            umma_commit(&o_full[p]);
+            need_o1 = false;
+            continue;
+          }
+          // S[q] held the masked scores of tile i-1: its O1 must have read them
+          if (need_s && mbar_test_wait(&x_full[q], uq & 1) && mbar_test_wait(&y_full[q], uq & 1) &&
+              (i + 1 < 2 || mbar_test_wait(&o_full[q], (uq - 1) & 1))) {
+            TRACE(32 + i * 5 + 2);
+            issue_s(i + 1);
+            need_s = false;
+            continue;
+          }
+          if (clock64() - t0 > kWaitClocks) {
+            dead = 1;
+            atomicOr(fault, kFaultMmaWait);
+          }
         }
       }
     }
@@ -445,24 +491,22 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
         mbar_arrive(&ring_scaled[j]);
       }
       wait_or_fault(&sum_done, 0, &dead, fault, kFaultMmaWait);
+      if (tid == 64) TRACE(59);
       tc_fence_after_sync();
       if (row < D) {
-        float* out = a.totals + ((size_t)blockIdx.x * D + row) * E + half * kHalfE;
 #pragma unroll
         for (int c0 = 0; c0 < kHalfE; c0 += 32) {
           uint32_t r[32];
           tmem_ld32(t_l + lane_base + half * kHalfE + c0, r);
           tmem_ld_wait();
-#pragma unroll
-          for (int q = 0; q < 32; q += 4)
-            *reinterpret_cast<float4*>(out + c0 + q) = make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]),
-                                                                   __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
+          store_state32<D>(a.totals + (size_t)blockIdx.x * D * E, row, half * kHalfE + c0, r);
         }
       }
       __threadfence();
       tc_fence_before_sync();
       named_sync(1, kWorkers);
       if (tid == 64) st_volatile_u32(a.sync + kSyncFlags + blockIdx.x, step_s);
+      if (tid == 64) TRACE(60);
     }
     int i = 0;
     for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++i) {
@@ -474,15 +518,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
         // the state at the span border; the O2 MMA that read the operand tile of the previous item has
         // completed (its o2_full was waited for)
         if constexpr (!FUSED) {
-          if (row < D) {
-            const float4* src =
-                reinterpret_cast<const float4*>(a.p0 + ((size_t)w.it * D + row) * E + half * kHalfE);
-#pragma unroll
-            for (int j = 0; j < kHalfE / 4; ++j) {
-              const float4 v = src[j];
-              P[4 * j] = v.x, P[4 * j + 1] = v.y, P[4 * j + 2] = v.z, P[4 * j + 3] = v.w;
-            }
-          }
+          if (row < D) load_state<kHalfE, D, false>(a.p0 + (size_t)w.it * D * E, row, half * kHalfE, P);
         } else {
           const int sp_idx = w.it - w.bh * a.nspans;
           const size_t mine = (size_t)row * E + half * kHalfE;
@@ -499,36 +535,26 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
 #pragma unroll
             for (int j = 0; j < kHalfE; ++j) P[j] = 0.f;
           }
-          // totals of the spans before this one (each decayed to its own end)
-          for (int j = 0; j < sp_idx; ++j) {
-            if (tid == 64 && !dead) {
-              if (!wait_flag_eq(a.sync + kSyncFlags + w.bh * a.nspans + j, step_s, a.wait_clocks)) {
-                dead = 1;
-                atomicOr(fault, kFaultFlagWait);
-              }
-            }
-            named_sync(1, kWorkers);
-            if (row < D) {
-              const float dec = decay_pow(sl2, (sp_idx - 1 - j) * a.span * C);
-              const float4* src =
-                  reinterpret_cast<const float4*>(a.totals + (size_t)(w.bh * a.nspans + j) * D * E + mine);
-#pragma unroll
-              for (int q = 0; q < kHalfE / 4; ++q) {
-                const float4 v = __ldcg(src + q);
-                P[4 * q] = fmaf(dec, v.x, P[4 * q]), P[4 * q + 1] = fmaf(dec, v.y, P[4 * q + 1]);
-                P[4 * q + 2] = fmaf(dec, v.z, P[4 * q + 2]), P[4 * q + 3] = fmaf(dec, v.w, P[4 * q + 3]);
-              }
+          // totals of the spans before this one (each decayed to its own end); one thread per flag
+          if (tid - 64 < sp_idx && !dead) {
+            if (!wait_flag_eq(a.sync + kSyncFlags + w.bh * a.nspans + (tid - 64), step_s, a.wait_clocks)) {
+              dead = 1;
+              atomicOr(fault, kFaultFlagWait);
             }
           }
-          if (a.p0_save != nullptr && row < D) {
-            float4* dst = reinterpret_cast<float4*>(a.p0_save + (size_t)w.it * D * E + mine);
-#pragma unroll
-            for (int q = 0; q < kHalfE / 4; ++q) dst[q] = make_float4(P[4 * q], P[4 * q + 1], P[4 * q + 2], P[4 * q + 3]);
+          named_sync(1, kWorkers);
+          for (int j = 0; j < sp_idx; ++j) {
+            if (row < D)
+              fma_state<kHalfE, D>(a.totals + (size_t)(w.bh * a.nspans + j) * D * E, row, half * kHalfE,
+                                   decay_pow(sl2, (sp_idx - 1 - j) * a.span * C), P);
           }
         }
         if (row < D) write_state_operand<kHalfE>(sp, D, row, half * kHalfE, P);
         fence_async_smem();
         mbar_arrive(&p_ready);
+        if constexpr (FUSED) {   // kept for the backward pass
+          if (a.p0_save != nullptr && row < D) store_state<kHalfE, D>(a.p0_save + (size_t)w.it * D * E, row, half * kHalfE, P);
+        }
       }
       if (tid == 64) TRACE(1 + i * 6 + 0);
       wait_or_fault(&s_full[p], ph, &dead, fault, kFaultMmaWait);
@@ -539,18 +565,29 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       scale_row_pieces<WX / 16>(sy[p], row, half * (WX / 16), decay_pow(sl2, max(len - row, 0)), lane);
       fence_async_smem();
       mbar_arrive(&ys_ready);
-      // X is overwritten by the masked scores: O2 must have read it
-      wait_or_fault(&o2_full, one, &dead, fault, kFaultMmaWait);
       if (tid == 64) TRACE(1 + i * 6 + 2);
+      // masked scores, packed to bf16 in place: they are the A operand of O1 straight from tensor memory
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
-        const int col0 = half * 64 + cc * 32;
-        masked_store32(t_s[p] + lane_base + col0, sx[p], row, col0, sl2, lam);
+        uint32_t packed[16];
+        masked_pack32<false>(t_s[p] + lane_base + half * 64 + cc * 32, row, half * 64 + cc * 32, sl2, lam, packed);
+        tmem_st16(t_s[p] + lane_base + half * 64 + cc * 16, packed);
       }
-      fence_async_smem();
+      tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&sm_ready[p]);
       if (tid == 64) TRACE(1 + i * 6 + 3);
+      // O2's rows take their decay lambda^row in tensor memory; O1 then accumulates on top
+      wait_or_fault(&o2_full[p], ph, &dead, fault, kFaultMmaWait);
+      tc_fence_after_sync();
+      {
+        const float qd = decay_pow(sl2, row);
+#pragma unroll
+        for (int cc = 0; cc < WZ / 64; ++cc) scale_tmem32(t_o + lane_base + half * (WZ / 2) + cc * 32, qd);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&o2s_ready);
       // state: P <- lambda^len P + L
       wait_or_fault(&l_full, one, &dead, fault, kFaultMmaWait);
       tc_fence_after_sync();
@@ -580,18 +617,16 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
         }
       }
       if (tid == 64) TRACE(1 + i * 6 + 4);
-      // epilogue: OUT = O1 + lambda^row O2, staged in Y's buffer (the L MMA has read the scaled rows)
+      // epilogue: OUT staged in Y's buffer (the L MMA has read the scaled rows)
       wait_or_fault(&o_full[p], ph, &dead, fault, kFaultMmaWait);
       tc_fence_after_sync();
-      const float qd = decay_pow(sl2, row);
 #pragma unroll
       for (int cc = 0; cc < WZ / 64; ++cc) {
         const int col0 = half * (WZ / 2) + cc * 32;
-        stage_row32(t_s[p] + lane_base + col0, t_o2 + lane_base + col0, qd, sy[p], row, col0);
+        stage_row32(t_o + lane_base + col0, kNoAcc, 0.f, sy[p], row, col0);
       }
       tc_fence_before_sync();
-      mbar_arrive(&t_free[p]);
-      mbar_arrive(&o2_free);
+      mbar_arrive(&o_free);
       fence_async_smem();
       mbar_arrive(&staged[p]);
       if (tid == 64) TRACE(1 + i * 6 + 5);
@@ -600,6 +635,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
   tc_fence_before_sync();
   __syncthreads();
   if (tid == 64) TRACE(63);
+  if (tid == 64) GTRACE(58);
   if (warp == 2) tmem_dealloc(tmem, 512);
   if constexpr (FUSED) {
     // the last CTA to finish advances the launch counter: the flags of this launch are stale from then on
@@ -621,19 +657,29 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
 //   Dn <- lambda^len Dn + Q^T diag(lambda^r) dO          (len = tokens in the tile, 128 but for a ragged tail)
 //
 // Shared memory: Q, dO (single buffers), K, V (double buffered), the state operand: seven 32 KB buffers.
-//   K: tile -> (after phase A) S_m -> (after phase B) staging tile of dK
-//   V: tile -> (after phase A) dS_m -> (after phase B) staging tile of dV
-//   Q: tile -> (after phase B) rows scaled in place for the state update
-// Tensor memory: T_S (S, then S_m^T dO), T_dS (dS, then the state update L), T_dK (V Dn^T, scaled by
-// rows, += dS_m^T Q), T_X (K Dn).
+//   K : tile -> (after phase A) S_m  -> (after phase B) staging tile of dK
+//   V : tile -> (after phase A) dS_m -> (after phase B) staging tile of dV
+//   Dn: state operand -> (after phase A) row-scaled copy of Q for the state update -> new state operand
+// Tensor memory, four 128-column regions:
+//   T_S : S = Q K^T            -> (masked into shared memory) -> L = Q_s^T dO, the state update
+//   T_dS: dS = dO V^T          -> (masked into shared memory)
+//   T_dK: V Dn^T, rows scaled  -> += dS_m^T Q                  = dK
+//   T_dV: K Dn, rows scaled    -> += S_m^T dO                  = dV
+// Per tile the issuer runs phase A (four products), L as soon as the workers have copied Q and masked S,
+// and phase B once dS is masked and the two state products are scaled; the workers update the state
+// while phase B runs and then stage dK and dV for the TMA stores.
+//
+// FUSED: as in k_walk_out - the CTA first sums its span, T = sum_r lambda^(r - span start) q_r do_r^T,
+// through the K and V buffers, publishes it, adds up the totals of the LATER spans of its sequence (and
+// the incoming rank state) and walks; the outgoing rank state is the state after the first tile of the
+// sequence.
 // ---------------------------------------------------------------------------
-template <int D, int E>
+template <int D, int E, bool FUSED>
 __global__ void __launch_bounds__(320, 1) k_walk_dkv(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
     const __grid_constant__ CUtensorMap map_dk, const __grid_constant__ CUtensorMap map_dv,
-    const float* __restrict__ s, const float* __restrict__ dn0, int h, int n, int tiles, int span, int nspans,
-    int items, int32_t* fault) {
+    const __grid_constant__ WalkArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   uint8_t* sq = smem;
@@ -642,25 +688,31 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
   uint8_t* sv[2] = {smem + 4 * kBuf, smem + 5 * kBuf};
   uint8_t* sdn = smem + 6 * kBuf;
   __shared__ uint64_t kv_full[2], staged[2];
-  __shared__ uint64_t qdo_full, dn_ready, a_done, sm_ready, b_done, qs_ready, l_done, e_free, l_free;
-  __shared__ uint32_t tmem_slot;
+  __shared__ uint64_t qdo_full, dn_ready, a_done, ms_ready, sm_ready, b_done, l_done, e_free, l_free;
+  __shared__ uint64_t ring_full[2], ring_scaled[2], ring_empty[2], sum_done;   // the span-total phase
+  __shared__ uint32_t tmem_slot, step_s;
   __shared__ int dead;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int32_t* fault = a.fault;
   if (tid == 0) {
     dead = 0;
     for (int p = 0; p < 2; ++p) {
       mbar_init(&kv_full[p], 1);
       mbar_init(&staged[p], kWorkers);
+      mbar_init(&ring_full[p], 1);
+      mbar_init(&ring_scaled[p], kWorkers);
+      mbar_init(&ring_empty[p], 1);
     }
     mbar_init(&qdo_full, 1);
     mbar_init(&dn_ready, kWorkers);
     mbar_init(&a_done, 1);
+    mbar_init(&ms_ready, kWorkers);
     mbar_init(&sm_ready, kWorkers);
     mbar_init(&b_done, 1);
-    mbar_init(&qs_ready, kWorkers);
     mbar_init(&l_done, 1);
     mbar_init(&e_free, kWorkers);
     mbar_init(&l_free, kWorkers);
+    mbar_init(&sum_done, 1);
     fence_mbar_init();
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_k);
@@ -668,17 +720,50 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
     prefetch_tensormap(&map_do);
     prefetch_tensormap(&map_dk);
     prefetch_tensormap(&map_dv);
+    if constexpr (FUSED) step_s = a.nspans > 1 ? ld_volatile_u32(a.sync) + 1 : 0;
   }
   if (warp == 2) tmem_alloc(&tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
-  const uint32_t t_s = tmem, t_ds = tmem + 128, t_dk = tmem + 256, t_x = tmem + 384;
-  TileWalk w{items, nspans, span, tiles, 0, true};
+  if (tid == 64) TRACE(0);
+  if (tid == 64) GTRACE(57);
+  if (tid == 64) g_trace[blockIdx.x * 64 + 56] = 0;
+  const uint32_t t_s = tmem, t_ds = tmem + 128, t_dk = tmem + 256, t_dv = tmem + 384;
+  TileWalk w{a.items, a.nspans, a.span, a.tiles, 0, true};
+  bool sums = false;
+  int sum_t0 = 0, sum_t1 = 0, my_bh = 0, my_sp = 0;
+  if constexpr (FUSED) {
+    if (a.nspans > 1 && w.start(blockIdx.x, gridDim.x)) {
+      my_bh = w.bh;
+      my_sp = w.it - w.bh * a.nspans;
+      sum_t0 = w.t0;
+      sum_t1 = w.t1;
+      sums = my_sp > 0 || a.all_totals;
+    }
+  }
 
   if (warp == 0) {
     if (lane == 0) {
+      bool first_qdo_issued = false;
+      if (sums) {
+        // Q, dO of the first tile of the walk can come in during the sums
+        if (w.start(blockIdx.x, gridDim.x)) {
+          mbar_expect_tx(&qdo_full, C * (D + E) * 2);
+          tma_load_4d(sq, &map_q, &qdo_full, 0, w.t * C, 0, w.bh);
+          tma_load_4d(sdo, &map_do, &qdo_full, 0, w.t * C, 0, w.bh);
+          first_qdo_issued = true;
+        }
+        for (int t = sum_t0, g = 0; t < sum_t1; ++t, ++g) {
+          const int j = g & 1;
+          if (g >= 2) wait_or_fault(&ring_empty[j], ((g >> 1) - 1) & 1, &dead, fault, kFaultMmaWait);
+          mbar_expect_tx(&ring_full[j], C * (D + E) * 2);
+          tma_load_4d(sk[j], &map_q, &ring_full[j], 0, t * C, 0, my_bh);
+          tma_load_4d(sv[j], &map_do, &ring_full[j], 0, t * C, 0, my_bh);
+        }
+        wait_or_fault(&sum_done, 0, &dead, fault, kFaultMmaWait);   // the MMAs have read every ring stage
+      }
       int i = 0;
       int out_row[2] = {0, 0}, out_bh[2] = {0, 0};
       for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++i) {
@@ -694,10 +779,15 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
         mbar_expect_tx(&kv_full[p], C * (D + E) * 2);
         tma_load_4d(sk[p], &map_k, &kv_full[p], 0, w.t * C, 0, w.bh);
         tma_load_4d(sv[p], &map_v, &kv_full[p], 0, w.t * C, 0, w.bh);
-        if (i >= 1) wait_or_fault(&l_done, (i - 1) & 1, &dead, fault, kFaultMmaWait);  // Q, dO of tile i-1 are read
-        mbar_expect_tx(&qdo_full, C * (D + E) * 2);
-        tma_load_4d(sq, &map_q, &qdo_full, 0, w.t * C, 0, w.bh);
-        tma_load_4d(sdo, &map_do, &qdo_full, 0, w.t * C, 0, w.bh);
+        if (i >= 1) {   // Q, dO of tile i-1 are read: by phase B and by L
+          wait_or_fault(&b_done, (i - 1) & 1, &dead, fault, kFaultMmaWait);
+          wait_or_fault(&l_done, (i - 1) & 1, &dead, fault, kFaultMmaWait);
+        }
+        if (i >= 1 || !first_qdo_issued) {
+          mbar_expect_tx(&qdo_full, C * (D + E) * 2);
+          tma_load_4d(sq, &map_q, &qdo_full, 0, w.t * C, 0, w.bh);
+          tma_load_4d(sdo, &map_do, &qdo_full, 0, w.t * C, 0, w.bh);
+        }
         out_row[p] = w.t * C;
         out_bh[p] = w.bh;
       }
@@ -712,33 +802,46 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      if (sums) {
+        for (int t = sum_t0, g = 0; t < sum_t1; ++t, ++g) {
+          const int j = g & 1;
+          wait_or_fault(&ring_scaled[j], (g >> 1) & 1, &dead, fault, kFaultTmaWait);
+          tc_fence_after_sync();
+          umma_gemm(t_s, Operand{smem_u32(sk[j]), C, true}, Operand{smem_u32(sv[j]), C, true}, E, C / 16, g > 0);
+          umma_commit(&ring_empty[j]);
+        }
+        umma_commit(&sum_done);
+      }
       int i = 0;
       for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++i) {
         const int p = i & 1, ph = (i >> 1) & 1, one = i & 1;
+        // phase A.  The state tile as [N = d rows] x [K = e columns] (V Dn^T) and as [K = d rows] x
+        // [N = e columns] (K Dn); T_dK, T_dV were drained by the previous epilogue, T_S by the state update
         wait_or_fault(&kv_full[p], ph, &dead, fault, kFaultTmaWait);
         wait_or_fault(&dn_ready, one, &dead, fault, kFaultMmaWait);
         if (i >= 1) {
-          wait_or_fault(&e_free, one ^ 1, &dead, fault, kFaultMmaWait);  // T_S, T_dK, T_X of tile i-1 are drained
-          wait_or_fault(&l_free, one ^ 1, &dead, fault, kFaultMmaWait);  // T_dS of tile i-1 is drained
+          wait_or_fault(&e_free, one ^ 1, &dead, fault, kFaultMmaWait);
+          wait_or_fault(&l_free, one ^ 1, &dead, fault, kFaultMmaWait);
         }
         tc_fence_after_sync();
-        // the state tile as [N = d rows] x [K = e columns] (V Dn^T) and as [K = d rows] x [N = e columns] (K Dn)
         umma_gemm(t_dk, Operand{smem_u32(sv[p]), C, false}, Operand{smem_u32(sdn), D, false}, D, E / 16, false);
-        umma_gemm(t_x, Operand{smem_u32(sk[p]), C, false}, Operand{smem_u32(sdn), D, true}, E, D / 16, false);
+        umma_gemm(t_dv, Operand{smem_u32(sk[p]), C, false}, Operand{smem_u32(sdn), D, true}, E, D / 16, false);
         wait_or_fault(&qdo_full, one, &dead, fault, kFaultTmaWait);
         tc_fence_after_sync();
         umma_gemm(t_s, Operand{smem_u32(sq), C, false}, Operand{smem_u32(sk[p]), C, false}, C, D / 16, false);
         umma_gemm(t_ds, Operand{smem_u32(sdo), C, false}, Operand{smem_u32(sv[p]), C, false}, C, E / 16, false);
         umma_commit(&a_done);
+        // L = Q_s^T dO over S's columns: the scaled copy of Q is in the state operand's buffer, S is masked
+        wait_or_fault(&ms_ready, one, &dead, fault, kFaultMmaWait);
+        tc_fence_after_sync();
+        umma_gemm(t_s, Operand{smem_u32(sdn), C, true}, Operand{smem_u32(sdo), C, true}, E, C / 16, false);
+        umma_commit(&l_done);
+        // phase B
         wait_or_fault(&sm_ready, one, &dead, fault, kFaultMmaWait);
         tc_fence_after_sync();
-        umma_gemm(t_dk, Operand{smem_u32(sv[p]), C, true}, Operand{smem_u32(sq), C, true}, D, C / 16, true);   // += dS_m^T Q
-        umma_gemm(t_s, Operand{smem_u32(sk[p]), C, true}, Operand{smem_u32(sdo), C, true}, E, C / 16, false);   // S_m^T dO
+        umma_gemm(t_dk, Operand{smem_u32(sv[p]), C, true}, Operand{smem_u32(sq), C, true}, D, C / 16, true);    // += dS_m^T Q
+        umma_gemm(t_dv, Operand{smem_u32(sk[p]), C, true}, Operand{smem_u32(sdo), C, true}, E, C / 16, true);   // += S_m^T dO
         umma_commit(&b_done);
-        wait_or_fault(&qs_ready, one, &dead, fault, kFaultMmaWait);
-        tc_fence_after_sync();
-        umma_gemm(t_ds, Operand{smem_u32(sq), C, true}, Operand{smem_u32(sdo), C, true}, E, C / 16, false);     // Q_s^T dO
-        umma_commit(&l_done);
       }
     }
   } else {
@@ -748,65 +851,131 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     constexpr int kHalfE = E / 2;
     float Dn[kHalfE];  // this thread's part of the suffix state: row `row`, columns [half * E/2, (half+1) * E/2)
+    float sl2 = 0.f, lam = 1.f;
+    if (sums) {
+      sl2 = a.s[my_bh % a.h] * kLog2e;
+      for (int t = sum_t0, g = 0; t < sum_t1; ++t, ++g) {
+        const int j = g & 1;
+        wait_or_fault(&ring_full[j], (g >> 1) & 1, &dead, fault, kFaultTmaWait);
+        scale_row_pieces<D / 16>(sk[j], row, half * (D / 16), decay_pow(sl2, (t - sum_t0) * C + row), lane);
+        fence_async_smem();
+        mbar_arrive(&ring_scaled[j]);
+      }
+      wait_or_fault(&sum_done, 0, &dead, fault, kFaultMmaWait);
+      if (tid == 64) TRACE(59);
+      tc_fence_after_sync();
+      if (row < D) {
+#pragma unroll
+        for (int c0 = 0; c0 < kHalfE; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(t_s + lane_base + half * kHalfE + c0, r);
+          tmem_ld_wait();
+          store_state32<D>(a.totals + (size_t)blockIdx.x * D * E, row, half * kHalfE + c0, r);
+        }
+      }
+      __threadfence();
+      tc_fence_before_sync();
+      named_sync(1, kWorkers);
+      if (tid == 64) st_volatile_u32(a.sync + kSyncFlags + blockIdx.x, step_s);
+      if (tid == 64) TRACE(60);
+    }
     int i = 0;
     for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++i) {
       const int p = i & 1, one = i & 1;
-      const float sl2 = s[w.bh % h] * kLog2e;
-      const float lam = exp2f(-sl2);
-      const int len = min(C, n - w.t * C);
+      const int len = min(C, a.n - w.t * C);
       if (w.first_of_item()) {
-        if (row < D) {
-          const float4* src = reinterpret_cast<const float4*>(dn0 + ((size_t)w.it * D + row) * E + half * kHalfE);
+        sl2 = a.s[w.bh % a.h] * kLog2e;
+        lam = exp2f(-sl2);
+        if constexpr (!FUSED) {
+          if (row < D) load_state<kHalfE, D, false>(a.p0 + (size_t)w.it * D * E, row, half * kHalfE, Dn);
+        } else {
+          const int sp_idx = w.it - w.bh * a.nspans;
+          const int span_end = min(w.t1 * C, a.n);
+          const size_t mine = (size_t)row * E + half * kHalfE;
+          // incoming rank state, decayed from the end of the sequence to the end of the span
+          if (a.x_in != nullptr && row < D) {
+            const float dec = decay_pow(sl2, a.n - span_end);
+            const float4* src = reinterpret_cast<const float4*>(a.x_in + (size_t)w.bh * D * E + mine);
 #pragma unroll
-          for (int j = 0; j < kHalfE / 4; ++j) {
-            const float4 v = src[j];
-            Dn[4 * j] = v.x, Dn[4 * j + 1] = v.y, Dn[4 * j + 2] = v.z, Dn[4 * j + 3] = v.w;
+            for (int j = 0; j < kHalfE / 4; ++j) {
+              const float4 v = src[j];
+              Dn[4 * j] = dec * v.x, Dn[4 * j + 1] = dec * v.y, Dn[4 * j + 2] = dec * v.z, Dn[4 * j + 3] = dec * v.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < kHalfE; ++j) Dn[j] = 0.f;
           }
-#pragma unroll
-          for (int j = 0; j < kHalfE; j += 8)
-            *reinterpret_cast<uint4*>(sdn + tile_offset(row, half * kHalfE + j, D)) =
-                make_uint4(pack_bf16(Dn[j], Dn[j + 1]), pack_bf16(Dn[j + 2], Dn[j + 3]),
-                           pack_bf16(Dn[j + 4], Dn[j + 5]), pack_bf16(Dn[j + 6], Dn[j + 7]));
+          // totals of the spans after this one (each decayed to its own start); one thread per flag
+          if (tid - 64 < a.nspans - 1 - sp_idx && !dead) {
+            if (!wait_flag_eq(a.sync + kSyncFlags + w.bh * a.nspans + sp_idx + 1 + (tid - 64), step_s, a.wait_clocks)) {
+              dead = 1;
+              atomicOr(fault, kFaultFlagWait);
+            }
+          }
+          named_sync(1, kWorkers);
+          for (int j = sp_idx + 1; j < a.nspans; ++j) {
+            if (row < D)
+              fma_state<kHalfE, D>(a.totals + (size_t)(w.bh * a.nspans + j) * D * E, row, half * kHalfE,
+                                   decay_pow(sl2, (j - sp_idx - 1) * a.span * C), Dn);
+          }
         }
+        // the phase-A MMAs that read the operand tile of the previous item have completed (a_done was waited for)
+        if (row < D) write_state_operand<kHalfE>(sdn, D, row, half * kHalfE, Dn);
         fence_async_smem();
         mbar_arrive(&dn_ready);
       }
+      if (tid == 64) TRACE(1 + i * 6 + 0);
       wait_or_fault(&a_done, one, &dead, fault, kFaultMmaWait);
+      wait_or_fault(&qdo_full, one, &dead, fault, kFaultTmaWait);  // completed long ago: makes Q's bytes visible here
+      if (tid == 64) TRACE(1 + i * 6 + 1);
       tc_fence_after_sync();
+      // row-scaled copy of Q over the state operand (phase A has read it), then S_m over the K tile
+      {
+        const float qd = decay_pow(sl2, row);
+        constexpr int kPieces = D / 16;
+        uint4 v[kPieces];
+#pragma unroll
+        for (int q = 0; q < kPieces; ++q) {
+          const int piece = half * kPieces + ((q + lane) & (kPieces - 1));
+          v[q] = *reinterpret_cast<const uint4*>(sq + (piece >> 3) * C * 128 + row * 128 + (piece & 7) * 16);
+        }
+#pragma unroll
+        for (int q = 0; q < kPieces; ++q) {
+          const int piece = half * kPieces + ((q + lane) & (kPieces - 1));
+          uint32_t* u = reinterpret_cast<uint32_t*>(&v[q]);
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u[t]));
+            u[t] = pack_bf16(f.x * qd, f.y * qd);
+          }
+          *reinterpret_cast<uint4*>(sdn + (piece >> 3) * C * 128 + row * 128 + (piece & 7) * 16) = v[q];
+        }
+      }
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int col0 = half * 64 + cc * 32;
         masked_store32(t_s + lane_base + col0, sk[p], row, col0, sl2, lam);    // S_m over the K tile
-        masked_store32(t_ds + lane_base + col0, sv[p], row, col0, sl2, lam);   // dS_m over the V tile
       }
+      fence_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&ms_ready);
+      if (tid == 64) TRACE(1 + i * 6 + 2);
       const float kd = decay_pow(sl2, max(len - row, 0));
 #pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int col0 = half * 64 + cc * 32;
+        masked_store32(t_ds + lane_base + col0, sv[p], row, col0, sl2, lam);   // dS_m over the V tile
+      }
+#pragma unroll
       for (int cc = 0; cc < D / 64; ++cc) scale_tmem32(t_dk + lane_base + half * (D / 2) + cc * 32, kd);
+#pragma unroll
+      for (int cc = 0; cc < E / 64; ++cc) scale_tmem32(t_dv + lane_base + half * (E / 2) + cc * 32, kd);
       tmem_st_wait();
       fence_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&sm_ready);
-      wait_or_fault(&b_done, one, &dead, fault, kFaultMmaWait);
-      wait_or_fault(&qdo_full, one, &dead, fault, kFaultTmaWait);  // completed long ago: makes Q's bytes visible here
-      tc_fence_after_sync();
-      scale_row_pieces<D / 16>(sq, row, half * (D / 16), decay_pow(sl2, row), lane);
-      fence_async_smem();
-      mbar_arrive(&qs_ready);
-      // epilogue: dK and dV staged over S_m and dS_m (both read by the phase-B MMAs)
-#pragma unroll
-      for (int cc = 0; cc < D / 64; ++cc) {
-        const int col0 = half * (D / 2) + cc * 32;
-        stage_row32(t_dk + lane_base + col0, kNoAcc, 0.f, sk[p], row, col0);
-      }
-#pragma unroll
-      for (int cc = 0; cc < E / 64; ++cc) {
-        const int col0 = half * (E / 2) + cc * 32;
-        stage_row32(t_s + lane_base + col0, t_x + lane_base + col0, kd, sv[p], row, col0);
-      }
-      tc_fence_before_sync();
-      mbar_arrive(&e_free);
-      fence_async_smem();
-      mbar_arrive(&staged[p]);
+      if (tid == 64) TRACE(1 + i * 6 + 3);
+      // state: Dn <- lambda^len Dn + L, while phase B runs
       wait_or_fault(&l_done, one, &dead, fault, kFaultMmaWait);
       tc_fence_after_sync();
       if (row < D) {
@@ -814,7 +983,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
 #pragma unroll
         for (int c0 = 0; c0 < kHalfE; c0 += 32) {
           uint32_t r[32];
-          tmem_ld32(t_ds + lane_base + half * kHalfE + c0, r);
+          tmem_ld32(t_s + lane_base + half * kHalfE + c0, r);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) Dn[c0 + j] = fmaf(lam_len, Dn[c0 + j], __uint_as_float(r[j]));
@@ -823,21 +992,53 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
       tc_fence_before_sync();
       mbar_arrive(&l_free);
       if (!w.last_of_item()) {
-        if (row < D) {
-#pragma unroll
-          for (int j = 0; j < kHalfE; j += 8)
-            *reinterpret_cast<uint4*>(sdn + tile_offset(row, half * kHalfE + j, D)) =
-                make_uint4(pack_bf16(Dn[j], Dn[j + 1]), pack_bf16(Dn[j + 2], Dn[j + 3]),
-                           pack_bf16(Dn[j + 4], Dn[j + 5]), pack_bf16(Dn[j + 6], Dn[j + 7]));
-        }
+        if (row < D) write_state_operand<kHalfE>(sdn, D, row, half * kHalfE, Dn);
         fence_async_smem();
         mbar_arrive(&dn_ready);
+      } else if constexpr (FUSED) {
+        // the state after the first tile of the sequence is the outgoing rank state
+        if (a.x_out != nullptr && w.t == 0 && row < D) {
+          float4* dst = reinterpret_cast<float4*>(a.x_out + (size_t)w.bh * D * E + (size_t)row * E + half * kHalfE);
+#pragma unroll
+          for (int q = 0; q < kHalfE / 4; ++q) dst[q] = make_float4(Dn[4 * q], Dn[4 * q + 1], Dn[4 * q + 2], Dn[4 * q + 3]);
+        }
       }
+      if (tid == 64) TRACE(1 + i * 6 + 4);
+      // epilogue: dK and dV staged over S_m and dS_m (both read by phase B)
+      wait_or_fault(&b_done, one, &dead, fault, kFaultMmaWait);
+      tc_fence_after_sync();
+#pragma unroll
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int col0 = half * (D / 2) + cc * 32;
+        stage_row32(t_dk + lane_base + col0, kNoAcc, 0.f, sk[p], row, col0);
+      }
+#pragma unroll
+      for (int cc = 0; cc < E / 64; ++cc) {
+        const int col0 = half * (E / 2) + cc * 32;
+        stage_row32(t_dv + lane_base + col0, kNoAcc, 0.f, sv[p], row, col0);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&e_free);
+      fence_async_smem();
+      mbar_arrive(&staged[p]);
+      if (tid == 64) TRACE(1 + i * 6 + 5);
     }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (tid == 64) TRACE(63);
+  if (tid == 64) GTRACE(58);
   if (warp == 2) tmem_dealloc(tmem, 512);
+  if constexpr (FUSED) {
+    if (tid == 0 && a.nspans > 1) {
+      __threadfence();
+      if (atomicAdd(a.sync + 1, 1u) == gridDim.x - 1) {
+        st_volatile_u32(a.sync + 1, 0u);
+        __threadfence();
+        st_volatile_u32(a.sync, step_s);
+      }
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -902,7 +1103,8 @@ cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, size_t smem, cudaS
   attr[0].id = cudaLaunchAttributeCooperative;
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = cooperative ? 1 : 0;
+  static const bool coop_off = [] { const char* v = getenv("LASP_B200_COOP"); return v && v[0] == '0'; }();
+  cfg.numAttrs = (cooperative && !coop_off) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
@@ -936,9 +1138,9 @@ cudaError_t launch_walk_out(const Dims& m, const void* x, const void* y, const v
   return launched(DQ ? "launch of the dq walk kernel" : "launch of the forward walk kernel");
 }
 
-template <int D, int E>
-cudaError_t launch_walk_dkv(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
-                            const float* s, const float* dn0, void* dk, void* dv, cudaStream_t st) {
+template <int D, int E, bool FUSED>
+cudaError_t launch_walk_dkv(const Dims& m, const void* q, const void* k, const void* v, const void* d_o, void* dk,
+                            void* dv, WalkArgs a, cudaStream_t st) {
   CUtensorMap mq, mk, mv, mdo, mdk, mdv;
   cudaError_t err;
   if ((err = seq_map(&mq, q, m, D, "q")) != cudaSuccess) return err;
@@ -947,13 +1149,21 @@ cudaError_t launch_walk_dkv(const Dims& m, const void* q, const void* k, const v
   if ((err = seq_map(&mdo, d_o, m, E, "do")) != cudaSuccess) return err;
   if ((err = seq_map(&mdk, dk, m, D, "dk")) != cudaSuccess) return err;
   if ((err = seq_map(&mdv, dv, m, E, "dv")) != cudaSuccess) return err;
-  int32_t* fault = nullptr;
-  if ((err = fault_word_address(&fault)) != cudaSuccess) return err;
+  if ((err = fault_word_address(&a.fault)) != cudaSuccess) return err;
   const size_t smem = (size_t)7 * kBuf + 1024;
-  if ((err = opt_in_smem(k_walk_dkv<D, E>, smem)) != cudaSuccess) return err;
-  const int items = m.b * m.h * m.nc;
-  k_walk_dkv<D, E><<<grid_for(items), 320, smem, st>>>(mq, mk, mv, mdo, mdk, mdv, s, dn0, m.h, m.n, m.tiles, m.span,
-                                                       m.nc, items, fault);
+  if ((err = opt_in_smem(k_walk_dkv<D, E, FUSED>, smem)) != cudaSuccess) return err;
+  a.h = m.h, a.n = m.n, a.tiles = m.tiles, a.span = m.span, a.nspans = m.nc, a.items = m.b * m.h * m.nc;
+  a.wait_clocks = kFlagWaitClocks;
+  const bool waits = FUSED && m.nc > 1;
+  if (waits && a.items > sm_count()) {
+    g_failed_step = "fused walk kernel: more spans than SMs";
+    return cudaErrorInvalidConfiguration;
+  }
+  if ((err = launch_kernel(k_walk_dkv<D, E, FUSED>, grid_for(a.items), smem, st, waits, mq, mk, mv, mdo, mdk, mdv, a)) !=
+      cudaSuccess) {
+    g_failed_step = "launch of the dk/dv walk kernel";
+    return err;
+  }
   return launched("launch of the dk/dv walk kernel");
 }
 
@@ -1005,7 +1215,19 @@ cudaError_t walk_bwd_dq(const Dims& m, const void* k, const void* v, const void*
 
 cudaError_t walk_bwd_dkv(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
                          const float* s, const float* suffix, void* dk, void* dv, cudaStream_t st) {
-#define LASP_CALL(DD, EE) launch_walk_dkv<DD, EE>(m, q, k, v, d_o, s, suffix, dk, dv, st)
+  WalkArgs a = {};
+  a.s = s, a.p0 = suffix;
+#define LASP_CALL(DD, EE) launch_walk_dkv<DD, EE, false>(m, q, k, v, d_o, dk, dv, a, st)
+  LASP_DISPATCH_DE(m, LASP_CALL);
+#undef LASP_CALL
+}
+
+cudaError_t walk_bwd_dkv_fused(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
+                               const float* s, const float* x_in, float* x_out, uint32_t* sync, float* totals,
+                               void* dk, void* dv, cudaStream_t st) {
+  WalkArgs a = {};
+  a.s = s, a.x_in = x_in, a.x_out = x_out, a.sync = sync, a.totals = totals;
+#define LASP_CALL(DD, EE) launch_walk_dkv<DD, EE, true>(m, q, k, v, d_o, dk, dv, a, st)
   LASP_DISPATCH_DE(m, LASP_CALL);
 #undef LASP_CALL
 }
