@@ -729,7 +729,6 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
   const uint32_t tmem = tmem_slot;
   if (tid == 64) TRACE(0);
   if (tid == 64) GTRACE(57);
-  if (tid == 64) g_trace[blockIdx.x * 64 + 56] = 0;
   const uint32_t t_s = tmem, t_ds = tmem + 128, t_dk = tmem + 256, t_dv = tmem + 384;
   TileWalk w{a.items, a.nspans, a.span, a.tiles, 0, true};
   bool sums = false;
