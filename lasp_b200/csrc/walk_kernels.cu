@@ -423,32 +423,14 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       }
       for (int i = 0; i < total; ++i) {
         const int p = i & 1, ph = (i >> 1) & 1, one = i & 1;
-        wait_or_fault(&p_ready, one, &dead, fault, kFaultMmaWait);
-        if (i >= 1) wait_or_fault(&o_free, one ^ 1, &dead, fault, kFaultMmaWait);   // the epilogue has drained O
-        TRACE(32 + i * 5 + 0);
-        tc_fence_after_sync();
-        if constexpr (!DQ)  // X P: the state tile as [K = d rows] x [N = e columns]
-          umma_gemm(t_o, Operand{smem_u32(sx[p]), C, false}, Operand{smem_u32(sp), D, true}, E, D / 16, false);
-        else                // X P^T: the state tile as [N = d rows] x [K = e columns]
-          umma_gemm(t_o, Operand{smem_u32(sx[p]), C, false}, Operand{smem_u32(sp), D, false}, D, E / 16, false);
-        umma_commit(&o2_full[p]);
-        // L = K^T diag(w) V (d x e), the scaled rows being Y's
-        wait_or_fault(&ys_ready, one, &dead, fault, kFaultMmaWait);
-        wait_or_fault(&z_full[p], ph, &dead, fault, kFaultTmaWait);
-        if (i >= 1) wait_or_fault(&l_free, one ^ 1, &dead, fault, kFaultMmaWait);
-        TRACE(32 + i * 5 + 1);
-        tc_fence_after_sync();
-        if constexpr (!DQ)
-          umma_gemm(t_l, Operand{smem_u32(sy[p]), C, true}, Operand{smem_u32(sz[p]), C, true}, E, C / 16, false);
-        else
-          umma_gemm(t_l, Operand{smem_u32(sz[p]), C, true}, Operand{smem_u32(sy[p]), C, true}, E, C / 16, false);
-        umma_commit(&l_full);
-        // O1 and the next S, whichever is ready first (O1 preferred)
         const int q = (i + 1) & 1, uq = (i + 1) >> 1;
-        bool need_o1 = true, need_s = i + 1 < total;
+        // the four products of the tile go out as their inputs become ready, in whatever order that is
+        bool need_o2 = true, need_l = true, need_o1 = true, need_s = i + 1 < total;
         const long long t0 = clock64();
-        while ((need_o1 || need_s) && !dead) {
-          if (need_o1 && mbar_test_wait(&sm_ready[p], ph) && mbar_test_wait(&o2s_ready, one)) {
+        while ((need_o2 || need_l || need_o1 || need_s) && !dead) {
+          // O1 = S_m Z on top of the row-scaled O2, the masked scores read from tensor memory
+          if (need_o1 && !need_o2 && mbar_test_wait(&sm_ready[p], ph) && mbar_test_wait(&o2s_ready, one) &&
+              mbar_test_wait(&z_full[p], ph)) {
             TRACE(32 + i * 5 + 3);
             tc_fence_after_sync();
             umma_gemm_ts(t_o, t_s[p], true, Operand{smem_u32(sz[p]), C, true}, WZ, true);
@@ -456,7 +438,32 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
             need_o1 = false;
             continue;
           }
-          // S[q] held the masked scores of tile i-1: its O1 must have read them
+          // L = K^T diag(w) V (d x e), the scaled rows being Y's; the state update has read the previous L
+          if (need_l && mbar_test_wait(&ys_ready, one) && mbar_test_wait(&z_full[p], ph) &&
+              (i < 1 || mbar_test_wait(&l_free, one ^ 1))) {
+            TRACE(32 + i * 5 + 1);
+            tc_fence_after_sync();
+            if constexpr (!DQ)
+              umma_gemm(t_l, Operand{smem_u32(sy[p]), C, true}, Operand{smem_u32(sz[p]), C, true}, E, C / 16, false);
+            else
+              umma_gemm(t_l, Operand{smem_u32(sz[p]), C, true}, Operand{smem_u32(sy[p]), C, true}, E, C / 16, false);
+            umma_commit(&l_full);
+            need_l = false;
+            continue;
+          }
+          // O2 = X op(P): the state operand of this tile is written, the epilogue has drained O
+          if (need_o2 && mbar_test_wait(&p_ready, one) && (i < 1 || mbar_test_wait(&o_free, one ^ 1))) {
+            TRACE(32 + i * 5 + 0);
+            tc_fence_after_sync();
+            if constexpr (!DQ)  // X P: the state tile as [K = d rows] x [N = e columns]
+              umma_gemm(t_o, Operand{smem_u32(sx[p]), C, false}, Operand{smem_u32(sp), D, true}, E, D / 16, false);
+            else                // X P^T: the state tile as [N = d rows] x [K = e columns]
+              umma_gemm(t_o, Operand{smem_u32(sx[p]), C, false}, Operand{smem_u32(sp), D, false}, D, E / 16, false);
+            umma_commit(&o2_full[p]);
+            need_o2 = false;
+            continue;
+          }
+          // S of the next tile; S[q] held the masked scores of tile i-1: its O1 must have read them
           if (need_s && mbar_test_wait(&x_full[q], uq & 1) && mbar_test_wait(&y_full[q], uq & 1) &&
               (i + 1 < 2 || mbar_test_wait(&o_full[q], (uq - 1) & 1))) {
             TRACE(32 + i * 5 + 2);
@@ -502,10 +509,12 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
           store_state32<D>(a.totals + (size_t)blockIdx.x * D * E, row, half * kHalfE + c0, r);
         }
       }
-      __threadfence();
       tc_fence_before_sync();
-      named_sync(1, kWorkers);
-      if (tid == 64) st_volatile_u32(a.sync + kSyncFlags + blockIdx.x, step_s);
+      named_sync(1, kWorkers);   // every worker's part of the total is written ...
+      if (tid == 64) {
+        __threadfence();         // ... and visible to the other CTAs before the flag is
+        st_volatile_u32(a.sync + kSyncFlags + blockIdx.x, step_s);
+      }
       if (tid == 64) TRACE(60);
     }
     int i = 0;
@@ -515,8 +524,31 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       if (w.first_of_item()) {
         sl2 = a.s[w.bh % a.h] * kLog2e;
         lam = exp2f(-sl2);
-        // the state at the span border; the O2 MMA that read the operand tile of the previous item has
-        // completed (its o2_full was waited for)
+      }
+      if (tid == 64) TRACE(1 + i * 6 + 0);
+      wait_or_fault(&s_full[p], ph, &dead, fault, kFaultMmaWait);
+      wait_or_fault(&y_full[p], ph, &dead, fault, kFaultTmaWait);  // completed long ago: makes Y's bytes visible here
+      if (tid == 64) TRACE(1 + i * 6 + 1);
+      tc_fence_after_sync();
+      // state chain first: scale Y's rows so that L can run under the mask
+      scale_row_pieces<WX / 16>(sy[p], row, half * (WX / 16), decay_pow(sl2, max(len - row, 0)), lane);
+      fence_async_smem();
+      mbar_arrive(&ys_ready);
+      if (tid == 64) TRACE(1 + i * 6 + 2);
+      // masked scores, packed to bf16 in place: they are the A operand of O1 straight from tensor memory
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t packed[16];
+        masked_pack32<false>(t_s[p] + lane_base + half * 64 + cc * 32, row, half * 64 + cc * 32, sl2, lam, packed);
+        tmem_st16(t_s[p] + lane_base + half * 64 + cc * 16, packed);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&sm_ready[p]);
+      if (tid == 64) TRACE(1 + i * 6 + 3);
+      if (w.first_of_item()) {
+        // the state at the span border (the score work above does not need it, so the wait for the other
+        // CTAs' totals hides behind it); the O2 MMA that read the operand tile of the previous item has completed
         if constexpr (!FUSED) {
           if (row < D) load_state<kHalfE, D, false>(a.p0 + (size_t)w.it * D * E, row, half * kHalfE, P);
         } else {
@@ -556,27 +588,6 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
           if (a.p0_save != nullptr && row < D) store_state<kHalfE, D>(a.p0_save + (size_t)w.it * D * E, row, half * kHalfE, P);
         }
       }
-      if (tid == 64) TRACE(1 + i * 6 + 0);
-      wait_or_fault(&s_full[p], ph, &dead, fault, kFaultMmaWait);
-      wait_or_fault(&y_full[p], ph, &dead, fault, kFaultTmaWait);  // completed long ago: makes Y's bytes visible here
-      if (tid == 64) TRACE(1 + i * 6 + 1);
-      tc_fence_after_sync();
-      // state chain first: scale Y's rows so that L can run under the mask
-      scale_row_pieces<WX / 16>(sy[p], row, half * (WX / 16), decay_pow(sl2, max(len - row, 0)), lane);
-      fence_async_smem();
-      mbar_arrive(&ys_ready);
-      if (tid == 64) TRACE(1 + i * 6 + 2);
-      // masked scores, packed to bf16 in place: they are the A operand of O1 straight from tensor memory
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t packed[16];
-        masked_pack32<false>(t_s[p] + lane_base + half * 64 + cc * 32, row, half * 64 + cc * 32, sl2, lam, packed);
-        tmem_st16(t_s[p] + lane_base + half * 64 + cc * 16, packed);
-      }
-      tmem_st_wait();
-      tc_fence_before_sync();
-      mbar_arrive(&sm_ready[p]);
-      if (tid == 64) TRACE(1 + i * 6 + 3);
       // O2's rows take their decay lambda^row in tensor memory; O1 then accumulates on top
       wait_or_fault(&o2_full[p], ph, &dead, fault, kFaultMmaWait);
       tc_fence_after_sync();
@@ -872,10 +883,12 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
           store_state32<D>(a.totals + (size_t)blockIdx.x * D * E, row, half * kHalfE + c0, r);
         }
       }
-      __threadfence();
       tc_fence_before_sync();
-      named_sync(1, kWorkers);
-      if (tid == 64) st_volatile_u32(a.sync + kSyncFlags + blockIdx.x, step_s);
+      named_sync(1, kWorkers);   // every worker's part of the total is written ...
+      if (tid == 64) {
+        __threadfence();         // ... and visible to the other CTAs before the flag is
+        st_volatile_u32(a.sync + kSyncFlags + blockIdx.x, step_s);
+      }
       if (tid == 64) TRACE(60);
     }
     int i = 0;
@@ -1089,21 +1102,16 @@ cudaError_t launch_span_totals(const Dims& m, const void* a, const void* bten, c
   return launched("launch of the span-total kernel");
 }
 
-// a launch whose CTAs wait for one another: all of them must be resident
+// The CTAs of a fused launch wait for one another's totals.  They are at most one per SM (the host side
+// checks), so all of them become resident as soon as whatever ran before has drained; their waits are
+// bounded all the same and report through the fault word.
 template <typename... KArgs, typename... Args>
-cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, size_t smem, cudaStream_t st, bool cooperative,
-                          Args... args) {
+cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, size_t smem, cudaStream_t st, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(320);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeCooperative;
-  attr[0].val.cooperative = 1;
-  cfg.attrs = attr;
-  static const bool coop_off = [] { const char* v = getenv("LASP_B200_COOP"); return v && v[0] == '0'; }();
-  cfg.numAttrs = (cooperative && !coop_off) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
@@ -1129,7 +1137,7 @@ cudaError_t launch_walk_out(const Dims& m, const void* x, const void* y, const v
     g_failed_step = "fused walk kernel: more spans than SMs";
     return cudaErrorInvalidConfiguration;
   }
-  if ((err = launch_kernel(k_walk_out<D, E, DQ, FUSED>, grid_for(a.items), smem, st, waits, mx, my, mz, mo, a)) !=
+  if ((err = launch_kernel(k_walk_out<D, E, DQ, FUSED>, grid_for(a.items), smem, st, mx, my, mz, mo, a)) !=
       cudaSuccess) {
     g_failed_step = "launch of a walk kernel";
     return err;
@@ -1158,7 +1166,7 @@ cudaError_t launch_walk_dkv(const Dims& m, const void* q, const void* k, const v
     g_failed_step = "fused walk kernel: more spans than SMs";
     return cudaErrorInvalidConfiguration;
   }
-  if ((err = launch_kernel(k_walk_dkv<D, E, FUSED>, grid_for(a.items), smem, st, waits, mq, mk, mv, mdo, mdk, mdv, a)) !=
+  if ((err = launch_kernel(k_walk_dkv<D, E, FUSED>, grid_for(a.items), smem, st, mq, mk, mv, mdo, mdk, mdv, a)) !=
       cudaSuccess) {
     g_failed_step = "launch of the dk/dv walk kernel";
     return err;
