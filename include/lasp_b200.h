@@ -37,7 +37,7 @@
 extern "C" {
 #endif
 
-#define LASP_B200_ABI_VERSION 1
+#define LASP_B200_ABI_VERSION 2
 
 /* the library is built with hidden visibility; only the entry points below are exported */
 #if defined(__GNUC__)
@@ -65,7 +65,7 @@ typedef enum { LASP_F32 = 0, LASP_BF16 = 1, LASP_F16 = 2 } lasp_dtype;
 typedef enum {
   LASP_PATH_AUTO = 0,
   LASP_PATH_SIMT = 1,   /* fp32 FFMA kernels: any dtype, d,e multiples of 16 up to 128, any n */
-  LASP_PATH_TENSOR = 2  /* tcgen05/TMEM/TMA kernels: bf16, d,e in {64,128}, n multiple of 128 */
+  LASP_PATH_TENSOR = 2  /* tcgen05/TMEM/TMA kernels: bf16, d,e in {64,128}, n >= 128 (a ragged tail is fine) */
 } lasp_path;
 
 typedef struct {
@@ -161,24 +161,25 @@ LASP_B200_API int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args*
 LASP_B200_API int lasp_b200_state_combine(int b, int h, int d, int e, int n, const float* s, const float* x_in,
                             const float* x_local, float* x_out, void* stream);
 
-/* ---- state relay over NVLink peer memory ------------------------------ */
-/* total = the rank's own contribution to the outgoing state: the decayed sum of
- * the local chunk states left in `ws` by lasp_b200_fwd_chunk_states (reverse =
- * 0) or lasp_b200_bwd_chunk_states (reverse = 1).  Equals kv_out / dkv_out of
- * the scan phase with a zero incoming state, without touching the chunk states.
- * Replaces kv[:, :, -1] of lasp/lasp_fuse_parallel.py:941. */
-LASP_B200_API int lasp_b200_state_total(const lasp_problem* p, const void* ws, size_t ws_bytes, const float* s, float* total,
-                          int reverse, void* stream);
-
-/* The state exchange of a sequence-parallel group as ONE kernel over
- * peer-mapped buffers.  Rank-to-rank passing,
+/* ---- state hand-over over NVLink peer memory --------------------------- */
+/* The state hand-over of a sequence-parallel group, one launch per rank and
+ * direction, over peer-mapped buffers.  Rank-to-rank passing,
  *     x_in(r+1) = exp(-s n) x_in(r) + total(r),
- * has the closed form x_in(r) = sum_{q<r} exp(-s n)^(r-1-q) total(q); the kernel
- * stores this rank's `total` into the receive slots of every rank after it in
- * the chain order (plain peer stores over NVLink) and sums what the ranks before
- * it stored here.  Replaces dist.recv / KV update / dist.send of
+ * has the closed form x_in(r) = sum_{q<r} exp(-s n)^(r-1-q) total(q).  Called
+ * between the chunk-state phase and the output / gradient phase IN PLACE OF the
+ * scan phase, the kernel
+ *   - reduces this rank's chunk states (in `ws`) to its total and stores it
+ *     into the receive slots of the ranks after it in the chain order (plain
+ *     peer stores over NVLink);
+ *   - waits for what the ranks before it stored here, sums it with the decay
+ *     powers (= the incoming rank state) and runs the scan with it, leaving
+ *     `ws` exactly as lasp_b200_fwd_scan / lasp_b200_bwd_scan would.
+ * A contribution whose decay power exp(-s n (r-1-q)) is below 1e-12 is neither
+ * sent nor awaited.  Replaces dist.recv / KV update / dist.send of
  * lasp/lasp_fuse_parallel.py:1095-1106 (forward) and :1129-1135 (backward: the
- * caller reverses the chain order) - one NVLink latency instead of ranks-1.
+ * caller reverses the chain order and sets `reverse`) - one NVLink latency
+ * instead of ranks-1 - together with _fwd_kv_reduce / _bwd_dkv_reduce
+ * (lasp/lasp_fuse_parallel.py:203-257, 607-662).
  * `position` is this rank's place in the chain order (0 sends only, ranks-1
  * receives only); peer_* arrays are indexed by position.  All pointers are
  * device pointers; peer_* point into other GPUs' memory mapped into this
@@ -190,16 +191,17 @@ LASP_B200_API int lasp_b200_state_total(const lasp_problem* p, const void* ws, s
  *   acks    : ranks x 8 words, 128 bytes apart  [destination][slice], written by destinations
  *   counters: 16 words, zeroed once; the kernel keeps the step number there, so
  *             a replayed CUDA graph needs no new arguments.
- * Waits give up after wait_clocks GPU clocks (0 = about two seconds) and set
- * bit 4 of the fault word (lasp_b200_read_status). */
+ * Waits give up after wait_clocks GPU clocks (0 = about ten seconds), set bit 4
+ * of the fault word (lasp_b200_read_status) and make the states they could not
+ * complete NaN, so that a late peer cannot pass for a delivered state. */
 typedef struct {
-  int32_t b, h, d, e, n;     /* state shape and the rank's local sequence length */
   int32_t ranks;             /* group size, 2..8 */
   int32_t position;          /* this rank's place in the chain order */
+  int32_t reverse;           /* 0: forward (KV, prefix scan); 1: backward (dKV, suffix scan) */
   int32_t reserved;
   const float* s;            /* h decay rates */
-  const float* total;        /* (b,h,d,e) fp32 from lasp_b200_state_total */
-  float* x_in;               /* (b,h,d,e) fp32 out: the incoming state; NULL when position == 0 */
+  void* ws;                  /* the forward / backward workspace after its chunk-state phase */
+  size_t ws_bytes;
   const void* my_slots;      /* local receive slots */
   const uint32_t* my_acks;   /* local acknowledgement words */
   uint32_t* counters;        /* local */
@@ -207,13 +209,17 @@ typedef struct {
   uint32_t* peer_acks[8];    /* acknowledgement words of each position (entries < position are written) */
   int64_t wait_clocks;
 } lasp_exchange_args;
-LASP_B200_API int lasp_b200_state_exchange(const lasp_exchange_args* a, void* stream);
+LASP_B200_API int lasp_b200_exchange_scan(const lasp_problem* p, const lasp_exchange_args* a, void* stream);
 
 /* Copies this device's sticky kernel-fault word to *status_host (synchronises
  * the stream) and clears it when clear != 0.  0 = no kernel reported a fault;
  * the tensor-core kernels set bits when one of their bounded waits (TMA
  * arrival, tcgen05 completion) runs out instead of spinning for ever. */
 LASP_B200_API int lasp_b200_read_status(int32_t* status_host, int clear, void* stream);
+/* The same word copied to PINNED host memory by an asynchronous copy on `stream`, without
+ * synchronising: the caller looks at *status_host_pinned once an event recorded behind this call
+ * has completed (how the operators notice a fault one step later without stalling the stream). */
+LASP_B200_API int lasp_b200_copy_status_async(int32_t* status_host_pinned, void* stream);
 
 /* Forward pass that allocates nothing and needs no workspace from the caller.
  * (No counterpart in the reference, whose launchers allocate with torch.)

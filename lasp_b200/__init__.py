@@ -9,4 +9,13 @@ from .lasp_naive import lasp_naive, lasp_naive_  # noqa: F401
 from .lightning_attention import lightning_attn, lightning_attn_  # noqa: F401
 from .utils import *  # noqa: F401,F403
 
+
+def check_faults(clear: bool = True) -> None:
+    """Synchronise the current CUDA stream and raise ``lasp_b200.engine.KernelFault`` if a kernel of the
+    library has given up on one of its bounded waits (for instance a sequence-parallel peer that never
+    delivered its state) since the last check.  The operators make this check themselves, one step late
+    and without stalling the stream; call it where a synchronisation is acceptable (end of a step)."""
+    from . import engine
+    engine.check_faults(clear)
+
 __version__ = "0.1.0"

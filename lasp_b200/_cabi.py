@@ -10,7 +10,7 @@ import ctypes as C
 import os
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "liblasp_b200.so")
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 # lasp_dtype / lasp_path / lasp_status of include/lasp_b200.h
 F32, BF16, F16 = 0, 1, 2
@@ -49,8 +49,9 @@ class BwdArgs(C.Structure):
 
 
 class ExchangeArgs(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in ("b", "h", "d", "e", "n", "ranks", "position", "reserved")] + \
-               [(n, C.c_void_p) for n in ("s", "total", "x_in", "my_slots", "my_acks", "counters")] + \
+    _fields_ = [(n, C.c_int32) for n in ("ranks", "position", "reverse", "reserved")] + \
+               [("s", C.c_void_p), ("ws", C.c_void_p), ("ws_bytes", C.c_size_t)] + \
+               [(n, C.c_void_p) for n in ("my_slots", "my_acks", "counters")] + \
                [("peer_slots", C.c_void_p * 8), ("peer_acks", C.c_void_p * 8), ("wait_clocks", C.c_int64)]
 
 
@@ -75,9 +76,9 @@ SIGNATURES = {
     "lasp_b200_backward": (C.c_int, [_PP, _BP, C.c_void_p]),
     "lasp_b200_state_combine": (C.c_int, [C.c_int] * 5 + [C.c_void_p] * 5),
     "lasp_b200_read_status": (C.c_int, [C.POINTER(C.c_int32), C.c_int, C.c_void_p]),
+    "lasp_b200_copy_status_async": (C.c_int, [C.c_void_p, C.c_void_p]),
     "lasp_b200_forward_static": (C.c_int, [_PP, _FP, C.c_void_p]),
-    "lasp_b200_state_total": (C.c_int, [_PP, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
-    "lasp_b200_state_exchange": (C.c_int, [C.POINTER(ExchangeArgs), C.c_void_p]),
+    "lasp_b200_exchange_scan": (C.c_int, [_PP, C.POINTER(ExchangeArgs), C.c_void_p]),
 }
 STATIC_SCRATCH_BYTES = 64 << 20  # LASP_B200_STATIC_SCRATCH_BYTES
 

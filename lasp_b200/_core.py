@@ -64,6 +64,14 @@ def _check_shapes(q, k, v, s):
         raise TypeError("q, k, v must share one dtype")
     if s.numel() != q.shape[1]:
         raise ValueError(f"decay tensor has {s.numel()} entries for {q.shape[1]} heads")
+    d, e = q.shape[-1], v.shape[-1]
+    for name, width in (("q/k", d), ("v", e)):
+        rest = width % MAX_HEAD_SLICE
+        if width % 16 or (width > MAX_HEAD_SLICE and rest and rest % 16):
+            raise ValueError(f"head dimension of {name} is {width}: it must be a multiple of 16 "
+                             f"(wider than {MAX_HEAD_SLICE}: cut in {MAX_HEAD_SLICE}-wide slices)")
+    if q.shape[0] * q.shape[1] > 65535:
+        raise ValueError(f"batch x heads = {q.shape[0] * q.shape[1]} exceeds 65535")
 
 
 class LightningAttention(torch.autograd.Function):
@@ -102,9 +110,12 @@ class SequenceParallelAttention(torch.autograd.Function):
     * ``overlap=False`` (lasp_naive, lasp_cache): the reference's order -
       blocking receive, all three kernels, blocking send (NCCL / gloo).
     * ``overlap=True`` with the peer-mapped exchange (the default on GPUs of
-      one node): chunk-state kernel -> this rank's total -> ONE exchange kernel
-      that stores the total into every later rank's memory over NVLink and
-      sums what earlier ranks stored here -> scan -> output kernel.
+      one node): chunk-state kernel -> ONE hand-over kernel that reduces this
+      rank's states to its total, stores it into the later ranks' memory over
+      NVLink, sums what earlier ranks stored here and runs the scan with it
+      -> output kernel.  A peer that never delivers makes the results NaN and
+      raises ``KernelFault`` at the start of the next call (or at
+      ``lasp_b200.check_faults()``).
     * ``overlap=True`` over NCCL (LASP_B200_TRANSPORT=nccl, or CPU tensors):
       post the receive, run the state-independent chunk-state kernel, wait,
       scan, post the send, run the output kernel.
@@ -129,11 +140,10 @@ class SequenceParallelAttention(torch.autograd.Function):
         exchange = comm.relay_for(group, KV.numel(), q.device) if (overlap and last > 0 and q.is_cuda) else None
 
         if exchange is not None:
-            fw = ENGINE.Forward(plan, q, k, v, s, kv_in=kv_in, kv_out=None)
+            ENGINE.fault_watch(q.device).poll()          # a fault of the previous step surfaces here
+            fw = ENGINE.Forward(plan, q, k, v, s)
             fw.chunk_states()
-            total = ENGINE.state_total(plan, fw.ws, s, reverse=False)
-            exchange.exchange(total, kv_in, s, n, backward=False)
-            fw.scan()
+            exchange.exchange_scan(plan, fw.ws, s, backward=False)
             fw.output()
         else:
             fw = ENGINE.Forward(plan, q, k, v, s, kv_in=kv_in, kv_out=KV if rank < last else None)
@@ -164,12 +174,11 @@ class SequenceParallelAttention(torch.autograd.Function):
         DKV, link, rank, last = ctx.DKV, ctx.link, ctx.rank, ctx.last
         dkv_in = DKV if rank < last else None
         if ctx.exchange is not None:
-            bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws, dkv_in=dkv_in, dkv_out=None)
+            bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws)
             bw.chunk_states()
-            total = ENGINE.state_total(ctx.plan, bw.ws, s, reverse=True)
-            ctx.exchange.exchange(total, dkv_in, s, q.shape[2], backward=True)
-            bw.scan()
+            ctx.exchange.exchange_scan(ctx.plan, bw.ws, s, backward=True)
             bw.grads()
+            ENGINE.fault_watch(q.device).arm(q.device)   # looked at when the next call starts
             return bw.dq, bw.dk, bw.dv, None, None, None, None
         bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws, dkv_in=dkv_in,
                              dkv_out=DKV if rank > 0 else None)

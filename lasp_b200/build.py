@@ -17,7 +17,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "liblasp_b200.so")
-SOURCES = ["api.cu", "simt_kernels.cu", "tensor_kernels.cu", "walk_kernels.cu", "relay_kernels.cu", "static_scratch.cu"]
+SOURCES = ["api.cu", "simt_kernels.cu", "fault_word.cu", "walk_kernels.cu", "relay_kernels.cu", "static_scratch.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -88,13 +88,13 @@ class StateLink:
 class NvlinkExchange:
     """Peer-mapped receive slots, flags and acknowledgement words of one
     sequence-parallel group for one state size, and the launcher of the
-    exchange kernel (``lasp_b200_state_exchange``).
+    hand-over kernel.
 
     The buffers come from torch's symmetric-memory allocator (a CUDA virtual
     memory allocation exported to the group's other ranks); the transfer itself
-    is done by the library's own kernel with plain peer stores - no NCCL call
-    is on the path, so a whole forward or backward can be captured in a CUDA
-    graph.  Each rank's buffer holds two regions (forward, backward), each:
+    is done by the library's own kernel (``lasp_b200_exchange_scan``) with plain
+    peer stores - no NCCL call is on the path, so a whole forward or backward
+    can be captured in a CUDA graph.  Each rank's buffer holds two regions (forward, backward), each:
         [0, 8K) acks [destination][slice]   [8K, 9K) counters
         [32K, ...) slots [parity][source][element] of 8-byte {value, step} words
     """
@@ -117,29 +117,33 @@ class NvlinkExchange:
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)   # every rank has zeroed its flags before any peer writes one
 
-    def exchange(self, total, x_in, s, n: int, backward: bool, wait_clocks: int = 0) -> None:
-        """Launch the exchange on the current stream.  Forward: states flow towards
-        higher ranks; backward: towards lower ranks.  ``x_in`` (b,h,d,e) receives the
-        incoming state; it is None on the rank that has nobody before it."""
+    def exchange_scan(self, plan, ws, s, backward: bool, wait_clocks: int | None = None) -> None:
+        """Launch the hand-over of one direction on the current stream, between the chunk-state phase and
+        the output / gradient phase of the call that owns ``ws`` and in place of its scan phase.
+        Forward: states flow towards higher ranks; backward: towards lower ranks."""
         from . import _cabi, engine
-        b, h, d, e = total.shape
-        assert b * h * d * e == self.elems
+        assert plan.b * plan.h * plan.d * plan.e == self.elems
         pos = self.size - 1 - self.rank if backward else self.rank
-        assert (x_in is not None) == (pos > 0)
         off = self.region if backward else 0
-        sl = s.reshape(-1).to(device=total.device, dtype=torch.float32).contiguous()
+        sl = s.reshape(-1).to(device=ws.device, dtype=torch.float32).contiguous()
         a = _cabi.ExchangeArgs()
-        a.b, a.h, a.d, a.e, a.n, a.ranks, a.position = b, h, d, e, n, self.size, pos
-        a.s, a.total = sl.data_ptr(), total.data_ptr()
-        a.x_in = x_in.data_ptr() if x_in is not None else None
+        a.ranks, a.position, a.reverse = self.size, pos, 1 if backward else 0
+        a.s, a.ws, a.ws_bytes = sl.data_ptr(), ws.data_ptr(), ws.numel()
         me = self.ptrs[self.rank] + off
         a.my_acks, a.counters, a.my_slots = me, me + 8192, me + self._HEADER
         for q in range(self.size):
             base = self.ptrs[self.size - 1 - q if backward else q] + off   # buffer of the rank at position q
             a.peer_acks[q], a.peer_slots[q] = base, base + self._HEADER
-        a.wait_clocks = wait_clocks
-        engine.state_exchange(a, total.device)
-        self._keep = (sl, total, x_in)   # alive until the next launch is enqueued on the same stream
+        a.wait_clocks = wait_timeout_clocks() if wait_clocks is None else wait_clocks
+        engine.exchange_scan(plan, a, ws.device)
+        self._keep = (sl, ws)   # alive until the next launch is enqueued on the same stream
+
+
+def wait_timeout_clocks() -> int:
+    """How long the hand-over kernel waits for a peer before it reports a fault, in GPU clocks: env
+    LASP_B200_EXCHANGE_TIMEOUT_MS (default 30 s, the order of a process-group timeout, not of a step)."""
+    ms = float(os.environ.get("LASP_B200_EXCHANGE_TIMEOUT_MS", "30000"))
+    return max(1, int(ms * 1.9e6))
 
 
 _relays = {}
@@ -153,20 +157,35 @@ def transport() -> str:
     return os.environ.get("LASP_B200_TRANSPORT", "auto")
 
 
+def _make_relay(group, elems: int, device):
+    return NvlinkExchange(group, elems, device)
+
+
 def relay_for(group, elems: int, device):
-    """The group's NvlinkExchange for this state size, or None when peer mapping
-    is not available (collective: every rank of the group must call it alike)."""
+    """The group's NvlinkExchange for this state size, or None when peer mapping is not available.
+    Collective: every rank of the group calls it alike, and the ranks AGREE on the outcome - if setting
+    the buffers up fails on any rank, all of them use NCCL send/recv (a rank on the other transport
+    would wait for words that never come)."""
     global _relay_unavailable
     if transport() == "nccl" or _relay_unavailable:
         return None
     key = (id(group), elems, torch.device(device).index)
     if key not in _relays:
+        relay, failure = None, None
         try:
-            _relays[key] = NvlinkExchange(group, elems, device)
+            relay = _make_relay(group, elems, device)
         except Exception as exc:  # noqa: BLE001
+            failure = exc
+        ok = torch.tensor([0 if relay is None else 1], dtype=torch.int32,
+                          device=device if dist.get_backend(group) == "nccl" else "cpu")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if not int(ok.item()):
             if transport() == "nvlink":
-                raise
-            warnings.warn(f"lasp_b200: peer-mapped state exchange unavailable ({exc}); using NCCL send/recv")
+                raise RuntimeError("lasp_b200: the peer-mapped state exchange could not be set up on every rank"
+                                   ) from failure
+            warnings.warn(f"lasp_b200: peer-mapped state exchange unavailable on some rank "
+                          f"({failure or 'another rank failed'}); every rank uses NCCL send/recv")
             _relay_unavailable = True
             return None
+        _relays[key] = relay
     return _relays[key]

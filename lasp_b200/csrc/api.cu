@@ -55,15 +55,8 @@ void bind_context_once() {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// LASP_B200_TENSOR_IMPL=tile selects the per-tile tensor-core kernels (one bf16 state per 128 tokens in
-// global memory) instead of the walk kernels; LASP_B200_SPAN_TILES=k fixes the span length.  Read once.
-bool tile_kernels_requested() {
-  static const bool on = [] {
-    const char* v = getenv("LASP_B200_TENSOR_IMPL");
-    return v && v[0] == 't';
-  }();
-  return on;
-}
+// LASP_B200_UNFUSED=1 runs a composite call as its separate phases; LASP_B200_SPAN_TILES=k fixes the span
+// length (experiments).  Read once.
 bool unfused_requested() {
   static const bool on = [] {
     const char* v = getenv("LASP_B200_UNFUSED");
@@ -103,11 +96,6 @@ int make_dims(const lasp_problem* p, lasp::Dims* m) {
     m->nc = (p->n + m->chunk - 1) / m->chunk;
     return LASP_OK;
   }
-  if (tile_kernels_requested() && lasp::tensor_tile_path_supported(*m)) {
-    m->chunk = lasp::kTensorTile;
-    m->nc = m->tiles;
-    return LASP_OK;
-  }
   // Spans: as few tiles per span as keeps the number of spans (= work items of the persistent kernels,
   // b*h per span index) within one CTA per SM; a sequence-rich problem gets one span per sequence.
   m->walk = 1;
@@ -125,8 +113,8 @@ int make_dims(const lasp_problem* p, lasp::Dims* m) {
 
 size_t workspace_bytes(const lasp::Dims& m) {
   size_t s = lasp::state_elems(m);
-  size_t bytes = s * 4;  // fp32 states (SIMT) or bf16 local + bf16 prefix states (TENSOR, per tile)
-  if (m.walk) bytes = lasp::kWalkSyncBytes + 2 * s * 4;
+  size_t bytes = 2 * s * 4;  // local + prefix states
+  if (m.walk) bytes += lasp::kWalkSyncBytes;
   return (bytes + 255) & ~(size_t)255;
 }
 
@@ -208,68 +196,42 @@ size_t lasp_b200_bwd_workspace_bytes(const lasp_problem* p) { return lasp_b200_f
 
 namespace {
 
-// Programmatic dependent launch between the three kernels of a composite call (tensor path only).
-// Off unless LASP_B200_PDL=1 until it has been verified on a GPU.
-bool chain_launches() {
-  static const bool on = [] {
-    const char* v = getenv("LASP_B200_PDL");
-    return v && v[0] == '1';
-  }();
-  return on;
+int fwd_chunk_states(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs) {
+  if (m.walk) return cuda_fail(lasp::walk_span_totals(m, a->k, a->v, a->s, lasp::ws_local(a->ws, m), false, cs));
+  return cuda_fail(lasp::simt_chunk_states(m, a->k, a->v, a->s, lasp::ws_local(a->ws, m), false, cs));
 }
 
-int fwd_chunk_states(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs, bool chained) {
-  if (m.walk) return cuda_fail(lasp::walk_span_totals(m, a->k, a->v, a->s, lasp::ws_walk_border(a->ws, m), false, cs));
-  if (m.path == LASP_PATH_TENSOR)
-    return cuda_fail(lasp::tensor_chunk_states(m, a->k, a->v, a->s, lasp::ws_local_bf16(a->ws), false, chained, cs));
-  return cuda_fail(lasp::simt_chunk_states(m, a->k, a->v, a->s, lasp::ws_states_f32(a->ws), false, cs));
+int fwd_scan(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs) {
+  return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_local(a->ws, m), lasp::ws_prefix(a->ws, m), a->kv_in, a->kv_out,
+                                     false, cs));
 }
 
-int fwd_scan(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs, bool chained) {
-  if (m.path == LASP_PATH_TENSOR && !m.walk)
-    return cuda_fail(lasp::scan_states_bf16(m, a->s, lasp::ws_local_bf16(a->ws), lasp::ws_states_bf16(a->ws, m),
-                                            a->kv_in, a->kv_out, false, chained, cs));
-  float* states = m.walk ? lasp::ws_walk_border(a->ws, m) : lasp::ws_states_f32(a->ws);
-  return cuda_fail(lasp::scan_states(m, a->s, states, a->kv_in, a->kv_out, false, cs));
-}
-
-int fwd_output(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs, bool chained) {
+int fwd_output(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs) {
   if (m.walk)
     return cuda_fail(lasp::walk_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_walk_border(a->ws, m), a->o, cs));
-  if (m.path == LASP_PATH_TENSOR)
-    return cuda_fail(lasp::tensor_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_states_bf16(a->ws, m), a->o, chained,
-                                             cs));
-  return cuda_fail(lasp::simt_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_states_f32(a->ws), a->o, cs));
+  return cuda_fail(lasp::simt_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_prefix(a->ws, m), a->o, cs));
 }
 
-int bwd_chunk_states(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs, bool chained) {
-  if (m.walk) return cuda_fail(lasp::walk_span_totals(m, a->q, a->d_o, a->s, lasp::ws_walk_border(a->ws, m), true, cs));
-  if (m.path == LASP_PATH_TENSOR)
-    return cuda_fail(lasp::tensor_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_local_bf16(a->ws), true, chained, cs));
-  return cuda_fail(lasp::simt_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_states_f32(a->ws), true, cs));
+int bwd_chunk_states(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs) {
+  if (m.walk) return cuda_fail(lasp::walk_span_totals(m, a->q, a->d_o, a->s, lasp::ws_local(a->ws, m), true, cs));
+  return cuda_fail(lasp::simt_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_local(a->ws, m), true, cs));
 }
 
-int bwd_scan(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs, bool chained) {
-  if (m.path == LASP_PATH_TENSOR && !m.walk)
-    return cuda_fail(lasp::scan_states_bf16(m, a->s, lasp::ws_local_bf16(a->ws), lasp::ws_states_bf16(a->ws, m),
-                                            a->dkv_in, a->dkv_out, true, chained, cs));
-  float* states = m.walk ? lasp::ws_walk_border(a->ws, m) : lasp::ws_states_f32(a->ws);
-  return cuda_fail(lasp::scan_states(m, a->s, states, a->dkv_in, a->dkv_out, true, cs));
+int bwd_scan(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs) {
+  return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_local(a->ws, m), lasp::ws_prefix(a->ws, m), a->dkv_in,
+                                     a->dkv_out, true, cs));
 }
 
-int bwd_grads(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs, bool chained) {
+int bwd_grads(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs) {
   if (m.walk) {
-    // dQ walks forward over the prefix states the forward pass left in its workspace; dK, dV walk backward
+    // dQ walks forward over the border states the forward pass left in its workspace; dK, dV walk backward
     int st = cuda_fail(lasp::walk_bwd_dq(m, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m), a->dq, cs));
     if (st != LASP_OK) return st;
     return cuda_fail(lasp::walk_bwd_dkv(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->ws, m), a->dk,
                                         a->dv, cs));
   }
-  if (m.path == LASP_PATH_TENSOR)
-    return cuda_fail(lasp::tensor_bwd_grads(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_states_bf16(a->fwd_ws, m),
-                                            lasp::ws_states_bf16(a->ws, m), a->dq, a->dk, a->dv, chained, cs));
-  return cuda_fail(lasp::simt_bwd_grads(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_states_f32(a->fwd_ws),
-                                        lasp::ws_states_f32(a->ws), a->dq, a->dk, a->dv, cs));
+  return cuda_fail(lasp::simt_bwd_grads(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_prefix(a->fwd_ws, m),
+                                        lasp::ws_prefix(a->ws, m), a->dq, a->dk, a->dv, cs));
 }
 
 }  // namespace
@@ -280,19 +242,19 @@ extern "C" {
 int lasp_b200_fwd_chunk_states(const lasp_problem* p, const lasp_fwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_fwd(p, a, &m, false);
-  return st != LASP_OK ? st : fwd_chunk_states(m, a, static_cast<cudaStream_t>(stream), false);
+  return st != LASP_OK ? st : fwd_chunk_states(m, a, static_cast<cudaStream_t>(stream));
 }
 
 int lasp_b200_fwd_scan(const lasp_problem* p, const lasp_fwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_fwd(p, a, &m, false);
-  return st != LASP_OK ? st : fwd_scan(m, a, static_cast<cudaStream_t>(stream), false);
+  return st != LASP_OK ? st : fwd_scan(m, a, static_cast<cudaStream_t>(stream));
 }
 
 int lasp_b200_fwd_output(const lasp_problem* p, const lasp_fwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_fwd(p, a, &m, true);
-  return st != LASP_OK ? st : fwd_output(m, a, static_cast<cudaStream_t>(stream), false);
+  return st != LASP_OK ? st : fwd_output(m, a, static_cast<cudaStream_t>(stream));
 }
 
 int lasp_b200_forward(const lasp_problem* p, const lasp_fwd_args* a, void* stream) {
@@ -303,29 +265,28 @@ int lasp_b200_forward(const lasp_problem* p, const lasp_fwd_args* a, void* strea
   if (fusable(m))
     return cuda_fail(lasp::walk_fwd_fused(m, a->q, a->k, a->v, a->s, a->kv_in, a->kv_out, lasp::ws_walk_sync(a->ws),
                                           lasp::ws_walk_totals(a->ws), lasp::ws_walk_border(a->ws, m), a->o, cs));
-  const bool chained = chain_launches() && m.path == LASP_PATH_TENSOR;
-  if ((st = fwd_chunk_states(m, a, cs, chained)) != LASP_OK) return st;
-  if ((st = fwd_scan(m, a, cs, chained)) != LASP_OK) return st;
-  return fwd_output(m, a, cs, chained);
+  if ((st = fwd_chunk_states(m, a, cs)) != LASP_OK) return st;
+  if ((st = fwd_scan(m, a, cs)) != LASP_OK) return st;
+  return fwd_output(m, a, cs);
 }
 
 // ---- backward -------------------------------------------------------------
 int lasp_b200_bwd_chunk_states(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_bwd(p, a, &m, false);
-  return st != LASP_OK ? st : bwd_chunk_states(m, a, static_cast<cudaStream_t>(stream), false);
+  return st != LASP_OK ? st : bwd_chunk_states(m, a, static_cast<cudaStream_t>(stream));
 }
 
 int lasp_b200_bwd_scan(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_bwd(p, a, &m, false);
-  return st != LASP_OK ? st : bwd_scan(m, a, static_cast<cudaStream_t>(stream), false);
+  return st != LASP_OK ? st : bwd_scan(m, a, static_cast<cudaStream_t>(stream));
 }
 
 int lasp_b200_bwd_grads(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_bwd(p, a, &m, true);
-  return st != LASP_OK ? st : bwd_grads(m, a, static_cast<cudaStream_t>(stream), false);
+  return st != LASP_OK ? st : bwd_grads(m, a, static_cast<cudaStream_t>(stream));
 }
 
 int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
@@ -342,10 +303,9 @@ int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stre
                                               lasp::ws_walk_sync(a->ws), lasp::ws_walk_totals(a->ws), a->dk, a->dv,
                                               cs));
   }
-  const bool chained = chain_launches() && m.path == LASP_PATH_TENSOR;
-  if ((st = bwd_chunk_states(m, a, cs, chained)) != LASP_OK) return st;
-  if ((st = bwd_scan(m, a, cs, chained)) != LASP_OK) return st;
-  return bwd_grads(m, a, cs, chained);
+  if ((st = bwd_chunk_states(m, a, cs)) != LASP_OK) return st;
+  if ((st = bwd_scan(m, a, cs)) != LASP_OK) return st;
+  return bwd_grads(m, a, cs);
 }
 
 int lasp_b200_state_combine(int b, int h, int d, int e, int n, const float* s, const float* x_in,
@@ -356,31 +316,34 @@ int lasp_b200_state_combine(int b, int h, int d, int e, int n, const float* s, c
   return cuda_fail(lasp::state_combine(b, h, d, e, n, s, x_in, x_local, x_out, static_cast<cudaStream_t>(stream)));
 }
 
-int lasp_b200_state_total(const lasp_problem* p, const void* ws, size_t ws_bytes, const float* s, float* total,
-                          int reverse, void* stream) {
+int lasp_b200_exchange_scan(const lasp_problem* p, const lasp_exchange_args* a, void* stream) {
   lasp::Dims m;
   int st = make_dims(p, &m);
   if (st != LASP_OK) return st;
-  if (!ws || !s || !total) return LASP_ERR_NULL;
-  if (!aligned16(ws) || !aligned16(total)) return LASP_ERR_ALIGN;
-  if (ws_bytes < workspace_bytes(m)) return LASP_ERR_WORKSPACE;
-  return cuda_fail(lasp::state_total(m, s, ws, total, reverse != 0, static_cast<cudaStream_t>(stream)));
-}
-
-int lasp_b200_state_exchange(const lasp_exchange_args* a, void* stream) {
-  if (!a || !a->s || !a->total || !a->counters) return LASP_ERR_NULL;
-  bind_context_once();
-  if (a->b <= 0 || a->h <= 0 || a->d <= 0 || a->e <= 0 || a->n <= 0 || (a->d * a->e) % 4) return LASP_ERR_SHAPE;
+  if (!a || !a->s || !a->ws || !a->counters) return LASP_ERR_NULL;
   if (a->ranks < 2 || a->ranks > 8 || a->position < 0 || a->position >= a->ranks) return LASP_ERR_SHAPE;
-  if ((a->position > 0) != (a->x_in != nullptr)) return LASP_ERR_NULL;
+  if ((m.d * m.e) % 4) return LASP_ERR_SHAPE;
   if (a->position > 0 && !a->my_slots) return LASP_ERR_NULL;
   if (a->position < a->ranks - 1 && !a->my_acks) return LASP_ERR_NULL;
   for (int q = 0; q < a->ranks; ++q) {
     if (q < a->position && !a->peer_acks[q]) return LASP_ERR_NULL;
     if (q > a->position && !a->peer_slots[q]) return LASP_ERR_NULL;
   }
-  if (!aligned16(a->total) || !aligned16(a->x_in) || !aligned16(a->my_slots)) return LASP_ERR_ALIGN;
-  return cuda_fail(lasp::state_exchange(*a, static_cast<cudaStream_t>(stream)));
+  if (!aligned16(a->ws) || !aligned16(a->my_slots)) return LASP_ERR_ALIGN;
+  if (a->ws_bytes < workspace_bytes(m)) return LASP_ERR_WORKSPACE;
+  return cuda_fail(lasp::exchange_scan(m, *a, lasp::ws_local(a->ws, m), lasp::ws_prefix(a->ws, m),
+                                       static_cast<cudaStream_t>(stream)));
+}
+
+int lasp_b200_copy_status_async(int32_t* status_host_pinned, void* stream) {
+  if (!status_host_pinned) return LASP_ERR_NULL;
+  bind_context_once();
+  int32_t* word = nullptr;
+  cudaError_t err = lasp::fault_word_address(&word);
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(status_host_pinned, word, sizeof(int32_t), cudaMemcpyDeviceToHost,
+                          static_cast<cudaStream_t>(stream));
+  return cuda_fail(err);
 }
 
 int lasp_b200_read_status(int32_t* status_host, int clear, void* stream) {

@@ -9,20 +9,19 @@
 
 namespace lasp {
 
-// Workspace layout (forward and backward use the same one): S*4 bytes with
-// S = b*h*nc*d*e, where nc is the number of states kept per sequence:
-//   SIMT path        : fp32 chunk states (b,h,nc,d,e), one per 64-token chunk:
-//                      local states after the chunk-state phase; the scan turns
-//                      them into prefix states in place
-//   TENSOR path, walk: one state per SPAN of `span` 128-token tiles (a few per
+// Workspace layout (forward and backward use the same one), with S = b*h*nc*d*e
+// and nc the number of states kept per sequence.  The chunk-state phase writes
+// the LOCAL states, the scan reads them and writes the PREFIX states (exclusive,
+// seeded with the incoming rank state) that the output / gradient kernels read:
+//   SIMT path        : one state per 64-token chunk, fp32 (b,h,nc,d,e):
+//                      [0, S*4) prefix states, [S*4, 2*S*4) local states
+//   TENSOR path      : one state per SPAN of `span` 128-token tiles (a few per
 //                      sequence; inside a span the state lives on chip):
 //                      [0, 4096)            words the CTAs of the fused kernels
 //                                           synchronise through (zeroed once by
 //                                           the caller, kept by the library)
-//                      [4096, 4096 + S*4)   fp32 span totals (fused kernels)
-//                      [4096 + S*4, + S*4)  fp32 states at the span borders
-//   TENSOR path, tile: [0, S*2) bf16 local states, one per 128-token tile,
-//                      [S*2, S*4) bf16 prefix states written by the scan
+//                      [4096, 4096 + S*4)   local states: fp32 span totals
+//                      [4096 + S*4, + S*4)  prefix states: fp32 states at the span borders
 // The running prefix inside the scan is always fp32.
 constexpr int kSimtChunk = 64;    // the reference's block size
 constexpr int kTensorTile = 128;  // one tcgen05 M=128 tile
@@ -33,9 +32,9 @@ struct Dims {
   int nc;     // states per sequence
   int dtype;
   int path;
-  int walk;   // tensor path: 1 = state carried on chip along a span, 0 = one state per tile
+  int walk;   // 1 on the tensor path: the state is carried on chip along a span of tiles
   int tiles;  // tensor path: 128-token tiles per sequence
-  int span;   // tensor path, walk: tiles per span (chunk = span * 128)
+  int span;   // tensor path: tiles per span (chunk = span * 128)
 };
 
 // SM count of the current device (cached per device ordinal)
@@ -60,20 +59,17 @@ inline float* ws_walk_border(void* ws, const Dims& m) {
 inline const float* ws_walk_border(const void* ws, const Dims& m) {
   return reinterpret_cast<const float*>(static_cast<const char*>(ws) + kWalkSyncBytes + state_elems(m) * 4);
 }
-inline float* ws_states_f32(void* ws) { return reinterpret_cast<float*>(static_cast<char*>(ws)); }
-inline const float* ws_states_f32(const void* ws) {
-  return reinterpret_cast<const float*>(static_cast<const char*>(ws));
+// where the chunk-state phase writes / where the scan writes and the output kernels read
+inline float* ws_local(void* ws, const Dims& m) {
+  return m.walk ? ws_walk_totals(ws) : reinterpret_cast<float*>(static_cast<char*>(ws) + state_elems(m) * 4);
 }
-// tensor path: bf16 local states at offset 0, bf16 prefix states after them
-inline __nv_bfloat16* ws_local_bf16(void* ws) { return reinterpret_cast<__nv_bfloat16*>(ws); }
-inline __nv_bfloat16* ws_states_bf16(void* ws, const Dims& m) {
-  return reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + state_elems(m) * 2);
+inline float* ws_prefix(void* ws, const Dims& m) {
+  return m.walk ? ws_walk_border(ws, m) : reinterpret_cast<float*>(ws);
 }
-inline const __nv_bfloat16* ws_states_bf16(const void* ws, const Dims& m) {
-  return reinterpret_cast<const __nv_bfloat16*>(static_cast<const char*>(ws) + state_elems(m) * 2);
+inline const float* ws_prefix(const void* ws, const Dims& m) {
+  return m.walk ? ws_walk_border(ws, m) : reinterpret_cast<const float*>(ws);
 }
-
-// bits of the sticky per-device fault word (tensor_kernels.cu owns the word)
+// bits of the sticky per-device fault word (fault_word.cu owns the word)
 enum : int32_t {
   kFaultNone = 0,
   kFaultTmaWait = 1,   // a bounded wait on a TMA mbarrier ran out
@@ -91,10 +87,8 @@ extern thread_local const char* g_failed_step;
 // ---- launchers implemented in the .cu files (return cudaError_t) -----------
 cudaError_t simt_chunk_states(const Dims& m, const void* a, const void* bten, const float* s, float* states,
                               bool backward, cudaStream_t st);
-cudaError_t scan_states(const Dims& m, const float* s, float* states, const float* x_in, float* x_out, bool reverse,
-                        cudaStream_t st);
-cudaError_t scan_states_bf16(const Dims& m, const float* s, const __nv_bfloat16* local, __nv_bfloat16* prefix,
-                             const float* x_in, float* x_out, bool reverse, bool chained, cudaStream_t st);
+cudaError_t scan_states(const Dims& m, const float* s, const float* local, float* prefix, const float* x_in,
+                        float* x_out, bool reverse, cudaStream_t st);
 cudaError_t simt_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
                             const float* prefix, void* o, cudaStream_t st);
 cudaError_t simt_bwd_grads(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
@@ -104,22 +98,11 @@ cudaError_t state_combine(int b, int h, int d, int e, int n, const float* s, con
                           const float* x_local, float* x_out, cudaStream_t st);
 
 // state relay (relay_kernels.cu)
-cudaError_t state_total(const Dims& m, const float* s, const void* local, float* total, bool reverse,
-                        cudaStream_t st);
-cudaError_t state_exchange(const lasp_exchange_args& a, cudaStream_t st);
+cudaError_t exchange_scan(const Dims& m, const lasp_exchange_args& a, const float* local, float* prefix,
+                          cudaStream_t st);
 
-// tcgen05 path (tensor_kernels.cu)
-// chained = the launch is one of the three of a composite forward / backward call: the kernels then use
-// programmatic dependent launch so that each starts while the one ahead drains
-cudaError_t tensor_chunk_states(const Dims& m, const void* a, const void* bten, const float* s,
-                                __nv_bfloat16* states, bool backward, bool chained, cudaStream_t st);
-cudaError_t tensor_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
-                              const __nv_bfloat16* prefix, void* o, bool chained, cudaStream_t st);
-cudaError_t tensor_bwd_grads(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
-                             const float* s, const __nv_bfloat16* prefix, const __nv_bfloat16* suffix, void* dq,
-                             void* dk, void* dv, bool chained, cudaStream_t st);
+// tcgen05 path
 bool tensor_path_supported(const Dims& m);
-bool tensor_tile_path_supported(const Dims& m);
 
 // tcgen05 path with the state carried on chip (walk_kernels.cu)
 cudaError_t walk_span_totals(const Dims& m, const void* a, const void* bten, const float* s, float* totals,

@@ -66,6 +66,12 @@ LASP_HD long long slot_offset(int parity, int ranks, int source, long long elems
 // index of the acknowledgement word for (position, slice) in a rank's ack array
 LASP_HD int ack_index(int position, int slice) { return (position * kSlices + slice) * kAckStride; }
 
+// A state that has to cross `hops` whole ranks of n tokens on its way arrives multiplied by
+// exp(-s n hops).  Below exp(-kDecayCutoff) (about 1e-12, far under the resolution of the fp32 sum it
+// would join) it is neither sent nor waited for; sender and receiver apply the same rule.
+constexpr float kDecayCutoff = 27.6f;
+LASP_HD bool reaches(float s_times_n, int hops) { return s_times_n * (float)hops <= kDecayCutoff; }
+
 // a pusher may overwrite the slot of parity (step & 1) once the step two before has been acknowledged
 LASP_HD bool needs_ack_wait(uint32_t step) { return step >= 3; }
 

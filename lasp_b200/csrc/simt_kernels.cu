@@ -87,67 +87,15 @@ __global__ void __launch_bounds__(NT) k_chunk_states(const T* __restrict__ A, co
 
 // ---------------------------------------------------------------------------
 // scan over chunks, elementwise in (d,e).  forward: exclusive prefix seeded
-// with x_in; reverse: exclusive suffix.  k_scan turns fp32 local states into
-// prefix states in place; k_scan_bf16 reads bf16 local states and writes bf16
-// prefix states into a second buffer (the tensor-core operand).  The running
-// value is fp32 in both.  Loads of a batch of chunks are issued before the
+// with x_in; reverse: exclusive suffix.  k_scan reads the fp32 local states
+// and writes the prefix states to a second array.  Loads of a batch of chunks are issued before the
 // dependent recurrence so that their latencies overlap.
 // ---------------------------------------------------------------------------
 constexpr int kScanBatch = 8;
 
-template <bool PDL>
-__global__ void __launch_bounds__(256) k_scan_bf16(const float* __restrict__ s,
-                                                   const __nv_bfloat16* __restrict__ local,
-                                                   __nv_bfloat16* __restrict__ prefix,
-                                                   const float* __restrict__ x_in, float* __restrict__ x_out, int h,
-                                                   int n, int de, int nc, int chunk, int reverse) {
-  if constexpr (PDL) {
-    // programmatic dependent launch: everything this kernel reads is written by the kernel ahead
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  }
-  const int bh = blockIdx.y;
-  const int el = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-  if (el >= de) return;
-  const float sh = s[bh % h];
-  const float full = expf(-sh * (float)chunk);
-  const float tail = expf(-sh * (float)(n - (nc - 1) * chunk));
-  float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (x_in) p = *reinterpret_cast<const float4*>(x_in + (size_t)bh * de + el);
-  const __nv_bfloat16* lbase = local + (size_t)bh * nc * de + el;
-  __nv_bfloat16* pbase = prefix + (size_t)bh * nc * de + el;
-  for (int i0 = 0; i0 < nc; i0 += kScanBatch) {
-    uint2 loc[kScanBatch];
-#pragma unroll
-    for (int u = 0; u < kScanBatch; ++u) {
-      const int i = i0 + u;
-      if (i < nc) loc[u] = *reinterpret_cast<const uint2*>(lbase + (size_t)(reverse ? nc - 1 - i : i) * de);
-    }
-#pragma unroll
-    for (int u = 0; u < kScanBatch; ++u) {
-      const int i = i0 + u;
-      if (i < nc) {
-        const int c = reverse ? nc - 1 - i : i;
-        __nv_bfloat162 lo = __floats2bfloat162_rn(p.x, p.y), hi = __floats2bfloat162_rn(p.z, p.w);
-        uint2 pk;
-        pk.x = *reinterpret_cast<uint32_t*>(&lo);
-        pk.y = *reinterpret_cast<uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(pbase + (size_t)c * de) = pk;
-        const float dec = (c == nc - 1) ? tail : full;
-        const float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&loc[u].x));
-        const float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&loc[u].y));
-        p.x = fmaf(dec, p.x, a.x);
-        p.y = fmaf(dec, p.y, a.y);
-        p.z = fmaf(dec, p.z, b.x);
-        p.w = fmaf(dec, p.w, b.y);
-      }
-    }
-  }
-  if (x_out) *reinterpret_cast<float4*>(x_out + (size_t)bh * de + el) = p;
-}
-
-__global__ void __launch_bounds__(256) k_scan(const float* __restrict__ s, float* __restrict__ states,
-                                              const float* __restrict__ x_in, float* __restrict__ x_out, int h,
+__global__ void __launch_bounds__(256) k_scan(const float* __restrict__ s, const float* __restrict__ local,
+                                              float* __restrict__ prefix, const float* __restrict__ x_in,
+                                              float* __restrict__ x_out, int h,
                                               int n, int de, int nc, int chunk, int reverse, int lane_rows,
                                               int cols) {
   const int bh = blockIdx.y;
@@ -161,7 +109,8 @@ __global__ void __launch_bounds__(256) k_scan(const float* __restrict__ s, float
   const float tail = expf(-sh * (float)last_len);
   float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
   if (x_in) p = *reinterpret_cast<const float4*>(x_in + (size_t)bh * de + ext);
-  float* base = states + (size_t)bh * nc * de + el;
+  const float* base = local + (size_t)bh * nc * de + el;
+  float* out = prefix + (size_t)bh * nc * de + el;
   for (int i0 = 0; i0 < nc; i0 += kScanBatch) {
     float4 loc[kScanBatch];
 #pragma unroll
@@ -175,7 +124,7 @@ __global__ void __launch_bounds__(256) k_scan(const float* __restrict__ s, float
       if (i < nc) {
         const int c = reverse ? nc - 1 - i : i;
         const float dec = (c == nc - 1) ? tail : full;
-        *reinterpret_cast<float4*>(base + (size_t)c * de) = p;
+        *reinterpret_cast<float4*>(out + (size_t)c * de) = p;
         p.x = fmaf(dec, p.x, loc[u].x);
         p.y = fmaf(dec, p.y, loc[u].y);
         p.z = fmaf(dec, p.z, loc[u].z);
@@ -478,37 +427,15 @@ cudaError_t simt_chunk_states(const Dims& m, const void* a, const void* bten, co
   return cudaGetLastError();
 }
 
-cudaError_t scan_states(const Dims& m, const float* s, float* states, const float* x_in, float* x_out, bool reverse,
-                        cudaStream_t st) {
+cudaError_t scan_states(const Dims& m, const float* s, const float* local, float* prefix, const float* x_in,
+                        float* x_out, bool reverse, cudaStream_t st) {
   const int de = m.d * m.e;
   dim3 grid((de / 4 + 255) / 256, m.b * m.h);
-  k_scan<<<grid, 256, 0, st>>>(s, states, x_in, x_out, m.h, m.n, de, m.nc, m.chunk, reverse ? 1 : 0, m.walk ? m.d : 0,
+  k_scan<<<grid, 256, 0, st>>>(s, local, prefix, x_in, x_out, m.h, m.n, de, m.nc, m.chunk, reverse ? 1 : 0, m.walk ? m.d : 0,
                                m.e);
   return cudaGetLastError();
 }
 
-cudaError_t scan_states_bf16(const Dims& m, const float* s, const __nv_bfloat16* local, __nv_bfloat16* prefix,
-                             const float* x_in, float* x_out, bool reverse, bool chained, cudaStream_t st) {
-  const int de = m.d * m.e;
-  dim3 grid((de / 4 + 127) / 128, m.b * m.h);
-  if (chained) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(128);
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t err = cudaLaunchKernelEx(&cfg, k_scan_bf16<true>, s, local, prefix, x_in, x_out, m.h, m.n, de, m.nc,
-                                         m.chunk, reverse ? 1 : 0);
-    return err != cudaSuccess ? err : cudaGetLastError();
-  }
-  k_scan_bf16<false><<<grid, 128, 0, st>>>(s, local, prefix, x_in, x_out, m.h, m.n, de, m.nc, m.chunk,
-                                           reverse ? 1 : 0);
-  return cudaGetLastError();
-}
 
 cudaError_t state_combine(int b, int h, int d, int e, int n, const float* s, const float* x_in,
                           const float* x_local, float* x_out, cudaStream_t st) {

@@ -128,15 +128,6 @@ __device__ __forceinline__ void named_sync(int id, int count) {
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
-// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization
-// attribute may start before the kernel ahead of it in the stream has finished.  wait: blocks the
-// calling thread until every earlier kernel has completed and its writes are visible.
-// launch_dependents: lets the kernel behind this one start once every CTA has called it (or exited).
-// Rule kept by every kernel here: trigger only AFTER the own wait, so that "the kernel ahead of me
-// has triggered" always implies "everything before it has completed".
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
 // makes generic-proxy writes to shared memory visible to the async proxy (TMA, tcgen05.mma)
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 

@@ -198,27 +198,16 @@ def state_combine(s, x_in, x_local, n: int, out=None):
     _require_cuda(x_local, x_in)
     b, h, d, e = x_local.shape
     out = out if out is not None else torch.empty_like(x_local)
-    _cabi.call("lasp_b200_state_combine", b, h, d, e, n, _ptr(_slopes(s, h, x_local.device)), _ptr(x_in),
-               _ptr(x_local), _ptr(out), _stream())
+    with _on_device(x_local.device):
+        _cabi.call("lasp_b200_state_combine", b, h, d, e, n, _ptr(_slopes(s, h, x_local.device)), _ptr(x_in),
+                   _ptr(x_local), _ptr(out), _stream())
     return out
 
 
-def state_total(plan: Plan, ws: torch.Tensor, s, reverse: bool, out=None):
-    """This rank's own contribution to the outgoing state, from the local chunk
-    states in ``ws`` (after the chunk-state phase, before the scan)."""
-    _require_cuda(ws)
-    out = out if out is not None else torch.empty(plan.b, plan.h, plan.d, plan.e, dtype=torch.float32,
-                                                  device=ws.device)
-    sl = _slopes(s, plan.h, ws.device)
-    with _on_device(ws.device):
-        _cabi.call("lasp_b200_state_total", C.byref(plan.problem), _ptr(ws), ws.numel(), _ptr(sl), _ptr(out),
-                   1 if reverse else 0, _stream())
-    return out
-
-
-def state_exchange(args: "_cabi.ExchangeArgs", device) -> None:
-    with _on_device(device), _traced("lasp_b200_state_exchange"):
-        _cabi.call("lasp_b200_state_exchange", C.byref(args), _stream())
+def exchange_scan(plan: Plan, args: "_cabi.ExchangeArgs", device) -> None:
+    """The state hand-over of one direction (see lasp_b200_exchange_scan in include/lasp_b200.h)."""
+    with _on_device(device), _traced("lasp_b200_exchange_scan"):
+        _cabi.call("lasp_b200_exchange_scan", C.byref(plan.problem), C.byref(args), _stream())
 
 
 def read_status(clear: bool = True) -> int:
@@ -226,3 +215,58 @@ def read_status(clear: bool = True) -> int:
     word = C.c_int32(0)
     _cabi.call("lasp_b200_read_status", C.byref(word), 1 if clear else 0, _stream())
     return word.value
+
+
+class KernelFault(_cabi.LaspStatusError):
+    """A kernel of the library gave up on a bounded wait (a peer that never delivered its state, a
+    copy or tensor-core operation that never completed): the results of that call are not valid."""
+
+    def __init__(self, word: int):
+        names = [n for bit, n in ((1, "TMA wait"), (2, "tensor-core wait"), (4, "peer state wait"),
+                                  (8, "span-total wait")) if word & bit]
+        RuntimeError.__init__(self, f"lasp_b200: a kernel reported a fault ({', '.join(names) or word}); "
+                                    "the outputs of that call are invalid")
+        self.status = -8
+        self.word = word
+
+
+def check_faults(clear: bool = True) -> None:
+    """Synchronise the current stream and raise KernelFault if any kernel of this device has reported
+    a fault since the word was last cleared."""
+    word = read_status(clear=clear)
+    if word:
+        raise KernelFault(word)
+
+
+class _FaultWatch:
+    """Notices a fault without stalling the stream: `arm()` enqueues a copy of the fault word to pinned
+    memory behind the work just launched; `poll()` (called at the start of the next operator call)
+    looks at it once that copy has completed, and raises."""
+
+    def __init__(self):
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event = None
+
+    def arm(self, device) -> None:
+        with _on_device(device):
+            _cabi.call("lasp_b200_copy_status_async", C.c_void_p(self.host.data_ptr()), _stream())
+            self.event = torch.cuda.Event()
+            self.event.record()
+
+    def poll(self) -> None:
+        if self.event is not None and self.event.query():
+            self.event = None
+            word = int(self.host.item())
+            if word:
+                self.host.zero_()
+                raise KernelFault(word)
+
+
+_watches = {}
+
+
+def fault_watch(device) -> _FaultWatch:
+    key = torch.device(device).index
+    if key not in _watches:
+        _watches[key] = _FaultWatch()
+    return _watches[key]

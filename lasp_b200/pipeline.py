@@ -1,9 +1,10 @@
 """A pre-planned forward + backward of the operator on fixed buffers.
 
 ``FixedStep`` binds one set of input/output tensors to the C-ABI launches of a
-forward and a backward pass - six kernels on a single device, plus the two
-state totals and the two state exchanges when the rank is part of a
-sequence-parallel group.  Nothing is allocated by ``run()``, and no NCCL call
+forward and a backward pass: on a single device three kernels on the tensor-core
+path (fused forward, dQ walk, fused dK/dV walk; six on the fp32 path); as a rank
+of a sequence-parallel group seven (span totals, hand-over + scan, walk, twice,
+the backward walk being two kernels).  Nothing is allocated by ``run()``, and no NCCL call
 is made, so the whole step can be captured in a CUDA graph and replayed.
 It issues exactly the launches the autograd functions of ``_core`` issue.
 """
@@ -28,16 +29,15 @@ class FixedStep:
             self.relay = comm.relay_for(group, b * h * d * e, q.device)
             if self.relay is None:
                 raise RuntimeError("FixedStep needs the peer-mapped relay transport (LASP_B200_TRANSPORT=nvlink)")
-        state = lambda: torch.empty(b, h, d, e, dtype=torch.float32, device=q.device)  # noqa: E731
-        self.kv_in = state() if self.rank > 0 else None
-        self.dkv_in = state() if self.rank < self.last else None
-        self.total_f, self.total_b = (state(), state()) if self.relay is not None else (None, None)
-        self.fw = engine.Forward(self.plan, q, k, v, s, kv_in=self.kv_in)
-        self.bw = engine.Backward(self.plan, q, k, v, do, s, self.fw.ws, dkv_in=self.dkv_in)
+        self.fw = engine.Forward(self.plan, q, k, v, s)
+        self.bw = engine.Backward(self.plan, q, k, v, do, s, self.fw.ws)
 
     @property
     def launches(self) -> int:
-        return 6 if self.relay is None else 10
+        tensor = self.plan.path_name == "tensor"
+        if self.relay is None:
+            return 3 if tensor else 6
+        return 7 if tensor else 6
 
     @property
     def outputs(self):
@@ -50,12 +50,8 @@ class FixedStep:
             bw.run()
             return
         fw.chunk_states()
-        engine.state_total(self.plan, fw.ws, self.s, reverse=False, out=self.total_f)
-        self.relay.exchange(self.total_f, self.kv_in, self.s, self.n, backward=False)
-        fw.scan()
+        self.relay.exchange_scan(self.plan, fw.ws, self.s, backward=False)
         fw.output()
         bw.chunk_states()
-        engine.state_total(self.plan, bw.ws, self.s, reverse=True, out=self.total_b)
-        self.relay.exchange(self.total_b, self.dkv_in, self.s, self.n, backward=True)
-        bw.scan()
+        self.relay.exchange_scan(self.plan, bw.ws, self.s, backward=True)
         bw.grads()

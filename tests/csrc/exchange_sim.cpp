@@ -4,7 +4,8 @@
 // All ranks' buffers live in this process.  Each step runs every rank's push
 // CTAs, then every rank's gather CTAs, thread by thread, exactly as the kernel
 // partitions them, and checks that
-//   * every destination word is written exactly once per step with the step number,
+//   * every destination word whose decay power is above the cut-off is written exactly once per step
+//     with the step number, and no other word is written or read,
 //   * every gathered element equals sum_q a^(me-1-q) total_q (same Horner order),
 //   * acknowledgements land in the words the pushers later wait on, and the wait
 //     of step s (>= 3) finds the value s-2 already there.
@@ -35,7 +36,7 @@ int main(int argc, char** argv) {
   const int steps = atoi(argv[3]);
   const int h = 3;
   const long long de = elems / 6 > 0 && (elems % 6 == 0) ? elems / 6 : elems;  // pretend b*h = 6 when it divides
-  const float s[3] = {0.0f, 0.001f, 0.01f};
+  const float s[3] = {0.0f, 0.001f, 0.15f};   // the last head reaches the next rank only (s n = 15 per hop... 2 hops = 30 > cut-off)
   const int n = 100;
   std::vector<Rank> R(ranks);
   for (auto& r : R) {
@@ -72,6 +73,7 @@ int main(int argc, char** argv) {
             for (int u = 0; u < 4; ++u) {
               const long long el = base + (long long)u * kThreads * kVec;
               if (el >= hi) continue;
+              if (!reaches(s[(el / de) % h] * (float)n, di)) continue;   // one head per group of kVec elements
               for (int j = 0; j < kVec; ++j) {
                 if (el + j >= elems) { printf("push out of range\n"); return 1; }
                 R[dst].slots[off + el + j] = Word{R[me].total[el + j], step};
@@ -84,7 +86,8 @@ int main(int argc, char** argv) {
     for (int me = 1; me < ranks; ++me)
       for (int q = 0; q < me; ++q)
         for (long long i = 0; i < elems; ++i)
-          if (R[me].writes[slot_offset(step_i & 1, ranks, q, elems) + i] != 1) {
+          if (R[me].writes[slot_offset(step_i & 1, ranks, q, elems) + i] !=
+              (reaches(s[(i / de) % h] * (float)n, me - 1 - q) ? 1 : 0)) {
             printf("rank %d: word of source %d element %lld written %d times\n", me, q, i,
                    R[me].writes[slot_offset(step_i & 1, ranks, q, elems) + i]);
             return 1;
@@ -106,6 +109,7 @@ int main(int argc, char** argv) {
               const float a = expf(-s[((el + j) / de) % h] * (float)n);
               float acc = 0.f;
               for (int q = 0; q < n_src; ++q) {
+                if (!reaches(s[((el + j) / de) % h] * (float)n, me - 1 - q)) { acc *= a; continue; }
                 const Word w = R[me].slots[off + (long long)q * elems + el + j];
                 if (w.step != step) { printf("rank %d: stale word (step %u, want %u)\n", me, w.step, step); return 1; }
                 acc = fmaf(a, acc, w.value);

@@ -62,8 +62,9 @@ def test_problem_validation(lib):
 
 def test_workspace_size(lib):
     p = _problem(n=200)  # 4 chunks of 64
-    assert lib.lasp_b200_fwd_workspace_bytes(C.byref(p)) == 2 * 3 * 4 * 64 * 64 * 4
-    assert lib.lasp_b200_bwd_workspace_bytes(C.byref(p)) == 2 * 3 * 4 * 64 * 64 * 4
+    # local + prefix states
+    assert lib.lasp_b200_fwd_workspace_bytes(C.byref(p)) == 2 * 2 * 3 * 4 * 64 * 64 * 4
+    assert lib.lasp_b200_bwd_workspace_bytes(C.byref(p)) == 2 * 2 * 3 * 4 * 64 * 64 * 4
     assert lib.lasp_b200_fwd_workspace_bytes(C.byref(_problem(d=20))) == 0
 
 
@@ -91,18 +92,22 @@ def test_operators_refuse_cpu_tensors():
 
 
 def test_exchange_argument_checks(lib):
-    a = _cabi.ExchangeArgs()
-    assert lib.lasp_b200_state_exchange(C.byref(a), None) == -1                      # NULL pointers
-    a.s, a.total, a.counters = 4096, 4096, 4096
-    a.b, a.h, a.d, a.e, a.n = 1, 1, 16, 16, 64
-    a.ranks, a.position = 9, 0
-    assert lib.lasp_b200_state_exchange(C.byref(a), None) == -2                      # more than 8 ranks
-    a.ranks, a.position = 4, 4
-    assert lib.lasp_b200_state_exchange(C.byref(a), None) == -2                      # position outside the group
-    a.ranks, a.position = 4, 1
-    assert lib.lasp_b200_state_exchange(C.byref(a), None) == -1                      # position > 0 needs x_in
-    a.x_in, a.my_slots = 4096, 4096
-    assert lib.lasp_b200_state_exchange(C.byref(a), None) == -1                      # missing ack / peer pointers
     p = _problem()
-    assert lib.lasp_b200_state_total(C.byref(p), None, 0, None, None, 0, None) == -1
-    assert lib.lasp_b200_state_total(C.byref(p), 4096, 16, 4096, 4096, 0, None) == -5   # workspace too small
+    a = _cabi.ExchangeArgs()
+    assert lib.lasp_b200_exchange_scan(C.byref(p), C.byref(a), None) == -1               # NULL pointers
+    assert lib.lasp_b200_exchange_scan(None, C.byref(a), None) == -1
+    a.s, a.ws, a.counters, a.ws_bytes = 4096, 4096, 4096, 1 << 40
+    a.ranks, a.position = 9, 0
+    assert lib.lasp_b200_exchange_scan(C.byref(p), C.byref(a), None) == -2               # more than 8 ranks
+    a.ranks, a.position = 4, 4
+    assert lib.lasp_b200_exchange_scan(C.byref(p), C.byref(a), None) == -2               # position outside the group
+    a.ranks, a.position = 4, 1
+    assert lib.lasp_b200_exchange_scan(C.byref(p), C.byref(a), None) == -1               # position > 0 needs its slots
+    a.my_slots = 4096
+    assert lib.lasp_b200_exchange_scan(C.byref(p), C.byref(a), None) == -1               # missing ack / peer pointers
+    a.my_acks = 4096
+    for q in range(4):
+        a.peer_acks[q], a.peer_slots[q] = 4096, 4096
+    a.ws_bytes = 16
+    assert lib.lasp_b200_exchange_scan(C.byref(p), C.byref(a), None) == -5               # workspace too small
+    assert lib.lasp_b200_copy_status_async(None, None) == -1
