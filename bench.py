@@ -1,22 +1,24 @@
 """Benchmark of the LASP linear-attention hot path (forward + backward).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config cfg1|cfg2|cfg3|cfg4-64|...]
 
-Workload (the headline configuration): per rank b=2, h=12, 2048 tokens, d=e=128, bf16,
-seeded synthetic N(0,1) inputs (q,k scaled by d^-0.5), slopes 2^(-8(i+1)/12).
-With N GPUs the N ranks form one sequence-parallel group (DP=1, SP=N; global
-sequence 2048*N) unless --dp says otherwise; per-rank work is fixed (weak
-scaling).  A step is one forward + one backward of the operator.
+Headline workload (--config cfg1, the default): per rank b=2, h=12, 2048 tokens, d=e=128, bf16, seeded
+synthetic N(0,1) inputs (q,k scaled by d^-0.5), slopes 2^(-8(i+1)/12).  With N GPUs the N ranks form one
+sequence-parallel group (DP=1, SP=N; global sequence 2048*N) unless --dp says otherwise; per-rank work is
+fixed (weak scaling).  A step is one forward + one backward of the operator.  The other configurations are
+the long-sequence and no-decay shapes (one rank's share of the sequence each); they print the same line.
 
 One JSON line is printed by rank 0:
-  value  - tokens/s with inputs resident in HBM (device-timed, max over ranks);
-           the inputs rotate over enough independent sets to exceed the L2;
-  e2e    - tokens/s through the public operator with pinned HOST buffers:
-           host->device copies of q,k,v,do and device->host copies of
-           o,dq,dk,dv are inside the timed region;
-  roofline     - the dominant kernel (backward gradients) against measured HBM peak;
-  cpu_baseline - the CPU oracle (a port of the reference's arithmetic; the
-           reference has no CPU implementation) on this box's host cores.
+  value  - tokens/s with inputs resident in HBM (device-timed, max over ranks); the inputs rotate over
+           enough independent sets to exceed the L2;
+  e2e    - tokens/s through the public operator with pinned HOST buffers: host->device copies of q,k,v,do
+           and device->host copies of o,dq,dk,dv are inside the timed region;
+  parity - (N > 1) max|x - ref|/max|ref| of O, dQ, dK, dV of one graph-path step and one public-operator
+           step against the CPU oracle's rank chain on three heads, max over ranks; the run fails above
+           the gate;
+  roofline     - the kernel with the largest share of the step against the measured HBM peak;
+  cpu_baseline - (N = 1) the CPU oracle (a port of the reference's arithmetic; the reference has no CPU
+           implementation) on this box's host cores.
 
 --impl reference times that CPU port alone, with all host threads.
 """
@@ -36,16 +38,36 @@ sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
-# headline configuration, per rank
-B, H, N_LOCAL, D, E = 2, 12, 2048, 128, 128
-METRIC = "fwd+bwd tokens/s, LASP linear attention (b=2/rank, h=12, 2048 tokens/rank, d=e=128)"
 UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
 L2_BYTES = 126e6
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (backward gradients) on this
-# workload, from one ncu capture: 75.7 MB read (q,k,v,do and the two state tensors) + 5.6 MB written back by
-# kernel end (most of dq,dk,dv still sits in L2)
-DOMINANT_KERNEL_TRAFFIC_BYTES = 81.3e6
+PARITY_GATE = 2e-2
+PARITY_HEADS = 3
+
+# name -> per-rank shape (b, h, n, d, e), slopes, scaling of q and k, feature map, description
+CONFIGS = {
+    "cfg1": dict(b=2, h=12, n=2048, d=128, e=128, slopes="baseline", scale_qk=True, feature_map=None,
+                 text="BASELINE config 1: lightning attention fwd+bwd, b=2/rank, h=12, 2048 tokens/rank, d=e=128, "
+                      "decay 2^(-8(i+1)/12)"),
+    "cfg2": dict(b=1, h=16, n=16384, d=128, e=128, slopes="baseline", scale_qk=True, feature_map=None,
+                 text="BASELINE config 2 (TNL-1B layer, b=1, h=16, d=e=128): one rank's 16384 tokens of the "
+                      "131072-token sequence at SP=8"),
+    "cfg2-sp1": dict(b=1, h=16, n=131072, d=128, e=128, slopes="baseline", scale_qk=True, feature_map=None,
+                     text="BASELINE config 2 (TNL-1B layer, b=1, h=16, d=e=128): the whole 131072-token sequence "
+                          "on one rank (SP=1)"),
+    "cfg3": dict(b=1, h=32, n=65536, d=128, e=128, slopes="baseline", scale_qk=True, feature_map=None,
+                 text="BASELINE config 3 (TNL-7B layer, b=1, h=32, d=e=128): one rank's 65536 tokens of the "
+                      "524288-token sequence at SP=8"),
+    "cfg4-64": dict(b=4, h=16, n=4096, d=64, e=64, slopes="zero", scale_qk=False, feature_map="elu1",
+                    text="BASELINE config 4 (no decay, elu(x)+1 on q,k, b=4, h=16), d=e=64: one rank's 4096 tokens "
+                         "of the 32768-token sequence at SP=8"),
+    "cfg4-128": dict(b=4, h=16, n=4096, d=128, e=128, slopes="zero", scale_qk=False, feature_map="elu1",
+                     text="BASELINE config 4 (no decay, elu(x)+1 on q,k, b=4, h=16), d=e=128: one rank's 4096 "
+                          "tokens of the 32768-token sequence at SP=8"),
+    "cfg4-256": dict(b=4, h=16, n=4096, d=256, e=256, slopes="zero", scale_qk=False, feature_map="elu1",
+                     text="BASELINE config 4 (no decay, elu(x)+1 on q,k, b=4, h=16), d=e=256 (128-wide slices of "
+                          "both head dimensions): one rank's 4096 tokens of the 32768-token sequence at SP=8"),
+}
 
 
 def env_int(name, default):
@@ -60,6 +82,17 @@ def measured_peaks():
         return float(p["hbm_gbs"]), float(p["bf16_tflops_sustained"]), "measured"
     except Exception:  # noqa: BLE001
         return FALLBACK_HBM_GBS, 1400.0, "fallback"
+
+
+def profiled_traffic(kernel: str):
+    """dram bytes per launch of `kernel` at the headline configuration, from the ncu capture summarised in
+    profiles/dram_traffic_cfg1.json (None when no capture of that kernel is recorded)."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic_cfg1.json")) as f:
+            rec = json.load(f)["kernels"].get(kernel)
+        return None if rec is None else float(rec["dram_bytes_read"]) + float(rec["dram_bytes_written"])
+    except Exception:  # noqa: BLE001
+        return None
 
 
 class ClockSampler:
@@ -100,31 +133,54 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
-def slopes(h):
+def slopes_for(cfg):
+    h = cfg["h"]
+    if cfg["slopes"] == "zero":
+        return torch.zeros(h, 1, 1)
     i = torch.arange(1, h + 1, dtype=torch.float64)
     return torch.pow(2.0, -8.0 * i / h).float().reshape(h, 1, 1)
 
 
-def make_set(seed, device, dtype, pinned=False):
+def feature(t, cfg):
+    return torch.nn.functional.elu(t) + 1.0 if cfg["feature_map"] == "elu1" else t
+
+
+def make_set(cfg, seed, device, dtype, pinned=False):
+    b, h, n, d, e = (cfg[x] for x in "bhnde")
     g = torch.Generator().manual_seed(seed)
-    q = torch.randn(B, H, N_LOCAL, D, generator=g) * D ** -0.5
-    k = torch.randn(B, H, N_LOCAL, D, generator=g) * D ** -0.5
-    v = torch.randn(B, H, N_LOCAL, E, generator=g)
-    do = torch.randn(B, H, N_LOCAL, E, generator=g)
+    scale = d ** -0.5 if cfg["scale_qk"] else 1.0
+    q = feature(torch.randn(b, h, n, d, generator=g), cfg) * scale
+    k = feature(torch.randn(b, h, n, d, generator=g), cfg) * scale
+    v = torch.randn(b, h, n, e, generator=g)
+    do = torch.randn(b, h, n, e, generator=g)
     ts = [t.to(dtype) for t in (q, k, v, do)]
     if pinned:
         return [t.pin_memory() for t in ts]
     return [t.to(device) for t in ts]
 
 
+def parity_piece(cfg, which, b_global, chunk, heads=None):
+    """The global tensors of the parity check are defined piecewise - one seeded draw per (tensor, global
+    batch row, rank chunk) - so that a rank generates its own chunk plus, for the oracle, the checked
+    heads of every chunk; no rank ever builds a global tensor."""
+    g = torch.Generator().manual_seed(((7 * 4 + which) * 4096 + b_global) * 64 + chunk)
+    width = cfg["d"] if which < 2 else cfg["e"]
+    t = torch.randn(cfg["h"], cfg["n"], width, generator=g)
+    if which < 2:
+        t = feature(t, cfg) * (cfg["d"] ** -0.5 if cfg["scale_qk"] else 1.0)
+    return t if heads is None else t[heads]
+
+
 # ---------------------------------------------------------------------------
 # reference arm / cpu baseline: the oracle on the host cores
 # ---------------------------------------------------------------------------
-def cpu_port_tokens_per_s(reps, warm=1):
+def cpu_port_tokens_per_s(cfg, reps, warm=1):
     from oracle import lasp_oracle as O
     torch.set_num_threads(os.cpu_count() or 1)
-    q, k, v, do = O.make_inputs(0, B, H, N_LOCAL, D, E)
-    s = O.baseline_slopes(H)
+    b, h, d, e = cfg["b"], cfg["h"], cfg["d"], cfg["e"]
+    n = min(cfg["n"], 2048)                      # a bounded sample: at most 2048 tokens of the rank's chunk
+    q, k, v, do = O.make_inputs(0, b, h, n, d, e, scale_qk=cfg["scale_qk"], feature_map=cfg["feature_map"])
+    s = slopes_for(cfg)
     for _ in range(warm):
         O.fwd_bwd(q, k, v, s, do)
     times = []
@@ -132,22 +188,21 @@ def cpu_port_tokens_per_s(reps, warm=1):
         t0 = time.perf_counter()
         O.fwd_bwd(q, k, v, s, do)
         times.append(time.perf_counter() - t0)
-    return B * N_LOCAL / statistics.median(times), torch.get_num_threads(), times
+    sample = (f"{reps} runs of b={b}, h={h}, {n} tokens, d={d}, e={e} in fp32 (blocked B=64 torch port of the "
+              f"reference's kernels, {torch.get_num_threads()} threads), median")
+    return b * n / statistics.median(times), torch.get_num_threads(), times, sample
 
 
-def run_reference(args):
-    rank = env_int("RANK", 0)
-    if rank != 0:
+def run_reference(args, cfg):
+    if env_int("RANK", 0) != 0:
         return
-    value, cores, times = cpu_port_tokens_per_s(args.steps, max(1, min(args.warmup, 2)))
-    sample = (f"each step = one rank's chunk (b={B},h={H},n={N_LOCAL},d=e={D}) in fp32, blocked (B=64) torch port "
-              f"of the reference's kernels; {args.steps} steps, median")
+    value, cores, times, sample = cpu_port_tokens_per_s(cfg, args.steps, max(1, min(args.warmup, 2)))
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "impl": "reference", "metric": metric_name(cfg), "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * statistics.median(times),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "BASELINE config 1 per-rank chunk on CPU", "b": B, "h": H, "n": N_LOCAL, "d": D,
-                   "e": E},
+        "config": {"workload": cfg["text"] + " - on the host cores", "b": cfg["b"], "h": cfg["h"],
+                   "n": min(cfg["n"], 2048), "d": cfg["d"], "e": cfg["e"]},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -155,47 +210,59 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def metric_name(cfg):
+    return (f"fwd+bwd tokens/s, LASP linear attention (b={cfg['b']}/rank, h={cfg['h']}, {cfg['n']} tokens/rank, "
+            f"d={cfg['d']}, e={cfg['e']})")
+
+
 # ---------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------
-def run_ours(args):
+def run_ours(args, cfg):
     import torch.distributed as dist
+    import lasp_b200
     from lasp_b200 import engine, lasp_fuse_parallel, lightning_attn
     from lasp_b200.utils import initialize_lasp
 
+    b, h, n, d, e = (cfg[x] for x in "bhnde")
     rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
+    torch.set_num_threads(max(1, (os.cpu_count() or 8) // world))
     dp = args.dp
     sp = world // dp
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
         initialize_lasp(dp, sp)
     dtype = torch.bfloat16
-    s = slopes(H).to(device)
+    s = slopes_for(cfg).to(device)
+    wide = d > 128 or e > 128                  # head dimensions cut in 128-wide slices by the operator
 
     # enough independent input sets that a step never finds its inputs in L2
-    set_bytes = (2 * D + 2 * E) * 2 * B * H * N_LOCAL
-    n_sets = max(2, int(L2_BYTES * 1.6 // set_bytes) + 1)
-    sets = [make_set(1000 * rank + i, device, dtype) for i in range(n_sets)]
+    set_bytes = (2 * d + 2 * e) * 2 * b * h * n
+    n_sets = max(2, min(6, int(L2_BYTES * 1.6 // set_bytes) + 1))
+    sets = [make_set(cfg, 1000 * rank + i, device, dtype) for i in range(n_sets)]
     for st in sets:
         for t in st[:3]:
             t.requires_grad_(True)
-    KV = torch.empty(B, H, D, E, device=device)
-    DKV = torch.empty(B, H, D, E, device=device)
+    KV = torch.empty(b, h, d, e, device=device)
+    DKV = torch.empty(b, h, d, e, device=device)
 
-    plan = engine.make_plan(B, H, N_LOCAL, D, E, dtype)
+    def operator(q, k, v):
+        return lasp_fuse_parallel(q, k, v, s, KV, DKV) if sp > 1 else lightning_attn(q, k, v, s)
+
+    plan = None if wide else engine.make_plan(b, h, n, d, e, dtype)
     graphs = []
     graph_note = "eager operator calls"
-    if not args.eager:
-        # the launches of a step (6 kernels; 10 with the two state totals and the two
-        # state exchanges of a sequence-parallel rank) go through the C ABI and are replayed
-        # from a CUDA graph, one graph per input set
-        from lasp_b200.pipeline import FixedStep
+    group = None
+    if world > 1:
         from lasp_b200.utils import get_sequence_parallel_group
-        group = get_sequence_parallel_group() if world > 1 else None
+        group = get_sequence_parallel_group()
+    if not args.eager and not wide:
+        # the launches of a step go through the C ABI and are replayed from a CUDA graph, one per input set
+        from lasp_b200.pipeline import FixedStep
         side = torch.cuda.Stream()
         try:
             fixed_steps = [FixedStep(q.detach(), k.detach(), v.detach(), do, s, group) for q, k, v, do in sets]
@@ -203,22 +270,9 @@ def run_ours(args):
         except Exception as exc:  # noqa: BLE001  (no peer-mapped exchange here: time the eager NCCL path)
             graph_note = f"eager operator calls ({type(exc).__name__}: {exc})"[:200]
             fixed_steps, usable = [], 0
-        if usable and world > 1:
-            # self-check of the exchange before anything is timed: one eager step; a bounded wait that ran out
-            # (fault word != 0 on any rank) sends every rank down the NCCL route instead
-            fixed_steps[0].run()
-            torch.cuda.synchronize()
-            if engine.read_status(clear=True) != 0:
-                usable = 0
-                graph_note = "eager operator calls over NCCL (the exchange self-check reported a fault)"
         flag = torch.tensor([usable], device=device)
         if world > 1:
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)      # all ranks take the same route
-        if world > 1 and not flag.item():
-            from lasp_b200 import comm
-            comm._relay_unavailable = True                   # the operators now use NCCL send/recv
-            if usable:
-                graph_note = "eager operator calls over NCCL (the exchange self-check failed on another rank)"
         for fixed in (fixed_steps if flag.item() else []):
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
@@ -232,17 +286,53 @@ def run_ours(args):
                 fixed.run()
             graphs.append((g, fixed))
 
+    # ---- parity before anything is timed (N > 1): graph path and public operator against the oracle chain
+    parity = None
+    if world > 1:
+        from oracle import lasp_oracle as O
+        from lasp_b200.pipeline import FixedStep
+        dp_rank, sp_rank = rank // sp, rank % sp
+        rows = [i * dp + dp_rank for i in range(b)]                      # batch interleaved over dp
+        mine = [torch.stack([parity_piece(cfg, w, bg, sp_rank) for bg in rows]).to(dtype).to(device) for w in range(4)]
+        heads = sorted({0, h // 2, h - 1})[:PARITY_HEADS]
+        glob = [torch.stack([torch.cat([parity_piece(cfg, w, bg, r, heads) for r in range(sp)], 1) for bg in rows])
+                .to(dtype).float() for w in range(4)]
+        outs, grads, _ = O.sp_chain(glob[0], glob[1], glob[2], slopes_for(cfg)[heads], glob[3], sp)
+        ref = dict(o=outs[sp_rank], dq=grads[sp_rank][0], dk=grads[sp_rank][1], dv=grads[sp_rank][2])
+        errs = {}
+
+        def record(tag, o, dq, dk, dv):
+            for name, t in (("o", o), ("dq", dq), ("dk", dk), ("dv", dv)):
+                errs[name] = max(errs.get(name, 0.0), O.max_rel_err(t[:, heads].float().cpu(), ref[name]))
+
+        if graphs:
+            step0 = FixedStep(mine[0], mine[1], mine[2], mine[3], s, group)
+            step0.run()
+            torch.cuda.synchronize()
+            record("graph path", *step0.outputs)
+        qp, kp, vp = (t.clone().requires_grad_(True) for t in mine[:3])
+        op = operator(qp, kp, vp)
+        op.backward(mine[3])
+        torch.cuda.synchronize()
+        record("operator", op.detach(), qp.grad, kp.grad, vp.grad)
+        lasp_b200.check_faults()
+        worst = torch.tensor([errs[k] for k in ("o", "dq", "dk", "dv")], device=device)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        parity = {k: float(x) for k, x in zip(("o", "dq", "dk", "dv"), worst.tolist())}
+        parity.update(gate=PARITY_GATE, heads=heads, reference="CPU oracle rank chain (fp32) on the bf16-rounded inputs",
+                      paths=["graph of C-ABI launches", "lasp_fuse_parallel"] if graphs else ["lasp_fuse_parallel"])
+        if max(worst.tolist()) > PARITY_GATE or any(x != x for x in worst.tolist()):
+            if rank == 0:
+                print(json.dumps({"error": "parity gate exceeded", "parity": parity}), flush=True)
+            raise SystemExit(3)
+
     def step(i):
         if graphs:
             graphs[i % n_sets][0].replay()
             return
         q, k, v, do = sets[i % n_sets]
         q.grad = k.grad = v.grad = None
-        if sp > 1:
-            o = lasp_fuse_parallel(q, k, v, s, KV, DKV)
-        else:
-            o = lightning_attn(q, k, v, s)
-        o.backward(do)
+        operator(q, k, v).backward(do)
 
     def sync_all():
         if world > 1:
@@ -253,7 +343,7 @@ def run_ours(args):
         step(i)
     sync_all()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    tokens_per_step = B * dp * N_LOCAL * sp
+    tokens_per_step = b * dp * n * sp
     with ClockSampler(local) as clocks:
         sync_all()
         start.record()
@@ -265,9 +355,9 @@ def run_ours(args):
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         ms_per_step = ms.item() / args.steps
-        # The timed region lasts a few milliseconds, too short for nvidia-smi to sample.  Keep the same
-        # steps running for about a second under the sampler: its clocks and throttle reasons are those of
-        # this load, and the longer window gives a sustained figure next to the timed one.
+        # The timed region can be too short for nvidia-smi to sample.  Keep the same steps running for about a
+        # second under the sampler: its clocks and throttle reasons are those of this load, and the longer
+        # window gives a sustained figure next to the timed one (the one to trust when they differ).
         extra = int(min(20000, max(args.steps, 1000.0 / max(ms_per_step, 1e-3))))
         t2 = torch.tensor([extra], device=device)
         if world > 1:
@@ -287,7 +377,7 @@ def run_ours(args):
                  "ms_per_step": ms_sus.item() / extra}
 
     # ---- end to end through the public operator with host buffers ---------
-    host_in = make_set(5000 + rank, device, dtype, pinned=True)
+    host_in = make_set(cfg, 5000 + rank, device, dtype, pinned=True)
     host_out = [torch.empty_like(t).pin_memory() for t in host_in]
     h2d = sum(t.numel() * t.element_size() for t in host_in)
     d2h = sum(t.numel() * t.element_size() for t in host_out)
@@ -295,7 +385,7 @@ def run_ours(args):
     def e2e_step():
         q, k, v, do = (t.to(device, non_blocking=True) for t in host_in)
         q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
-        o = lasp_fuse_parallel(q, k, v, s, KV, DKV) if sp > 1 else lightning_attn(q, k, v, s)
+        o = operator(q, k, v)
         o.backward(do)
         for dst, src in zip(host_out, (o.detach(), q.grad, k.grad, v.grad)):
             dst.copy_(src, non_blocking=True)
@@ -338,7 +428,7 @@ def run_ours(args):
                 in_ready[j].record(s_in)
             cur.wait_event(in_ready[j])
             q, k, v = (t.detach().requires_grad_(True) for t in dev_in[j][:3])
-            o = lasp_fuse_parallel(q, k, v, s, KV, DKV) if sp > 1 else lightning_attn(q, k, v, s)
+            o = operator(q, k, v)
             o.backward(dev_in[j][3])
             in_free[j].record(cur)
             outs = (o.detach(), q.grad, k.grad, v.grad)
@@ -353,55 +443,64 @@ def run_ours(args):
         cur.wait_stream(s_out)
         cur.wait_stream(s_in)
 
-    e2e_mode = "serial (copy in, compute, copy out)"
-    e2e_value = e2e_serial
+    e2e_modes = {"serial (copy in, compute, copy out)": e2e_serial}
     try:
         e2e_pipelined_loop()                           # warm-up of the streams and buffers
-        piped = timed(e2e_pipelined_loop)
-        if piped > e2e_value:
-            e2e_value, e2e_mode = piped, "copies overlapped with compute on side streams"
+        e2e_modes["copies overlapped with compute on side streams"] = timed(e2e_pipelined_loop)
     except Exception as exc:  # noqa: BLE001  (keep the serial number)
-        e2e_mode += f"; pipelined variant failed: {type(exc).__name__}"
+        e2e_modes[f"pipelined variant failed: {type(exc).__name__}"] = 0.0
+    e2e_mode = max(e2e_modes, key=e2e_modes.get)
+    e2e_value = e2e_modes[e2e_mode]
 
-    # ---- dominant kernel alone: backward gradients --------------------------
+    # ---- the kernels of a step one by one: which dominates, and its roofline ----
     hbm_peak, tensor_peak, peak_kind = measured_peaks()
-    fws, bws = [], []
-    for q, k, v, do in sets:
-        fw = engine.Forward(plan, q.detach(), k.detach(), v.detach(), s)
-        fw.run()
-        bw = engine.Backward(plan, q.detach(), k.detach(), v.detach(), do, s, fw.ws)
-        bw.chunk_states(), bw.scan()
-        fws.append(fw), bws.append(bw)
-    for bw in bws:
-        bw.grads()
-    torch.cuda.synchronize()
-    reps = 8 * n_sets
-
-    def launch_ms(fn):
-        """average device time of one launch: a graph of back-to-back launches rotating over the input sets"""
-        kg = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(kg):
-            for i in range(reps):
-                fn(i % n_sets)
-        kg.replay()
+    kernels, roofline = None, None
+    if not wide and plan.path_name == "tensor":
+        fws, bws = [], []
+        for q, k, v, do in sets:
+            fw = engine.Forward(plan, q.detach(), k.detach(), v.detach(), s)
+            fw.run()
+            bw = engine.Backward(plan, q.detach(), k.detach(), v.detach(), do, s, fw.ws)
+            bw.run()
+            fws.append(fw), bws.append(bw)
         torch.cuda.synchronize()
-        start.record()
-        kg.replay()
-        stop.record()
-        torch.cuda.synchronize()
-        return start.elapsed_time(stop) / reps
+        reps = 8 * n_sets
 
-    kernel_ms = launch_ms(lambda i: bws[i].grads())
-    phases = None
-    if args.phases:
-        phases = {name: 1e3 * launch_ms(fn) for name, fn in (
-            ("fwd_chunk_states_us", lambda i: fws[i].chunk_states()), ("fwd_scan_us", lambda i: fws[i].scan()),
-            ("fwd_output_us", lambda i: fws[i].output()), ("bwd_chunk_states_us", lambda i: bws[i].chunk_states()),
-            ("bwd_scan_us", lambda i: bws[i].scan()), ("bwd_grads_us", lambda i: bws[i].grads()))}
-    kernel_bytes = (4 * D + 3 * E) * 2 * B * H * N_LOCAL      # reads q,k,v,do; writes dq,dk,dv
-    achieved = kernel_bytes / (kernel_ms * 1e-3) / 1e9
-    step_bytes = (6 * D + 5 * E) * 2 * B * H * N_LOCAL
-    step_flops = (2 * 64 * (4 * D + 3 * E) + 12 * D * E) * B * H * N_LOCAL
+        def launch_us(fn):
+            """average device time of one launch: a graph of back-to-back launches rotating over the input sets"""
+            kg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(kg):
+                for i in range(reps):
+                    fn(i % n_sets)
+            kg.replay()
+            torch.cuda.synchronize()
+            start.record()
+            kg.replay()
+            stop.record()
+            torch.cuda.synchronize()
+            return 1e3 * start.elapsed_time(stop) / reps
+
+        per_token_head = {   # algorithmic bytes per token and head: every tensor of the launch touched once
+            "k_walk_out<fused> (forward: q,k,v -> o)": ((2 * d + 2 * e) * 2, lambda i: fws[i].run()),
+            "k_walk_out<dq> (do,v,k -> dq)": ((2 * d + 2 * e) * 2, lambda i: bws[i].dq_only()),
+            "k_walk_dkv<fused> (q,k,v,do -> dk,dv)": ((3 * d + 3 * e) * 2, lambda i: bws[i].dkv_only()),
+        }
+        kernels = {}
+        for name, (bytes_per, fn) in per_token_head.items():
+            us = launch_us(fn)
+            kernels[name] = {"us_per_launch": us, "algorithmic_bytes": bytes_per * b * h * n,
+                             "achieved_gbs": bytes_per * b * h * n / (us * 1e-6) / 1e9}
+        top = max(kernels, key=lambda k_: kernels[k_]["us_per_launch"])
+        step_bytes = (6 * d + 5 * e) * 2 * b * h * n
+        step_flops = (2 * 64 * (4 * d + 3 * e) + 12 * d * e) * b * h * n
+        traffic = profiled_traffic(top.split(" ")[0]) if args.config == "cfg1" else None
+        roofline = {"bound": "hbm", "kernel": top, "achieved": kernels[top]["achieved_gbs"], "peak": hbm_peak,
+                    "unit": "GB/s", "frac": kernels[top]["achieved_gbs"] / hbm_peak, "peak_source": peak_kind,
+                    "traffic": traffic, "traffic_source": "profiles/dram_traffic_cfg1.json" if traffic else None,
+                    "kernel_us": kernels[top]["us_per_launch"],
+                    "algorithmic_bytes_per_launch": kernels[top]["algorithmic_bytes"],
+                    "step_hbm_frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak,
+                    "step_tensor_frac": step_flops / (ms_per_step * 1e-3) / 1e12 / tensor_peak}
 
     fault_t = torch.tensor([engine.read_status(clear=False)], device=device)
     if world > 1:
@@ -412,37 +511,35 @@ def run_ours(args):
             dist.barrier()
             dist.destroy_process_group()
         return
-    cpu_value, cores, _ = cpu_port_tokens_per_s(3)
+    launches = graphs[0][1].launches if graphs else (3 if not wide else 3 * ((d + 127) // 128) * ((e + 127) // 128))
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "BASELINE config 1: lightning attention fwd+bwd, b=2/rank, h=12, 2048 tokens/rank, "
-                               "d=e=128, decay 2^(-8(i+1)/12)", "parallelism": f"dp{dp}xsp{sp}",
-                   "global_batch": B * dp, "global_seq_len": N_LOCAL * sp, "kernel_path": plan.path_name,
-                   "launch": f"cuda graph of the {graphs[0][1].launches} C-ABI launches" if graphs
+        "metric": metric_name(cfg), "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": cfg["text"], "name": args.config, "parallelism": f"dp{dp}xsp{sp}",
+                   "global_batch": b * dp, "global_seq_len": n * sp,
+                   "kernel_path": "tensor (128-wide slices)" if wide else plan.path_name,
+                   "launch": f"cuda graph of the {graphs[0][1].launches} C-ABI launches of a step" if graphs
                    else graph_note,
-                   "transport": ("nvlink exchange kernel" if graphs else "nccl or nvlink (operator default)")
+                   "transport": ("nvlink hand-over kernel" if graphs else "nccl or nvlink (operator default)")
                    if world > 1 else "none",
                    "l2": f"inputs rotate over {n_sets} independent sets ({n_sets * set_bytes / 1e6:.0f} MB) > L2"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "steps": e2e_steps, "mode": e2e_mode, "serial_value": e2e_serial},
-        "gpu_launches": (graphs[0][1].launches if graphs else 6) * args.steps,
+                "steps": e2e_steps, "mode": e2e_mode, "serial_value": e2e_serial,
+                "pcie_gbs_per_rank": (h2d + d2h) * e2e_value / tokens_per_step / 1e9},
+        "gpu_launches": launches * args.steps,
         "kernel_faults": fault_word,
         "clocks": clocks.summary(), "sustained": sustained,
-        "roofline": {"bound": "hbm", "kernel": f"bwd_grads ({plan.path_name})", "achieved": achieved,
-                     "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_kind,
-                     "traffic": DOMINANT_KERNEL_TRAFFIC_BYTES, "kernel_ms": kernel_ms,
-                     "algorithmic_bytes_per_launch": kernel_bytes,
-                     "step_hbm_frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak,
-                     "step_tensor_frac": step_flops / (ms_per_step * 1e-3) / 1e12 / tensor_peak},
-        "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"3 runs of one rank's chunk (b={B},h={H},n={N_LOCAL},d=e={D}) fp32, median"},
     }
+    if roofline is not None:
+        line["roofline"] = roofline
+        line["kernels"] = kernels
+    if parity is not None:
+        line["parity"] = parity
+    if world == 1:
+        cpu_value, cores, _, sample = cpu_port_tokens_per_s(cfg, 3)
+        line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
     print(json.dumps(line), flush=True)
-    if phases is not None:
-        print(json.dumps({"phases": phases, "note": "device time per launch of each of the six kernels, L2-cold"}),
-              flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -454,15 +551,16 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="cfg1", choices=sorted(CONFIGS))
     ap.add_argument("--dp", type=int, default=1, help="data-parallel size; sequence-parallel size = gpus / dp")
     ap.add_argument("--eager", action="store_true", help="time the public operator launch by launch (no CUDA graph)")
-    ap.add_argument("--phases", action="store_true", help="also print a second JSON line with the time of each kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    cfg = CONFIGS[args.config]
     if args.impl == "reference":
-        run_reference(args)
+        run_reference(args, cfg)
     else:
-        run_ours(args)
+        run_ours(args, cfg)
 
 
 if __name__ == "__main__":

@@ -137,7 +137,9 @@ LASP_B200_API int lasp_b200_fwd_scan(const lasp_problem* p, const lasp_fwd_args*
  * lasp/lasp_fuse_parallel.py:15-114,261-336 (== _fwd_kernel of
  * lasp/lightning_attention.py:6-83 and lasp/lasp_fuse.py:15-127). */
 LASP_B200_API int lasp_b200_fwd_output(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
-/* the three phases back to back: lasp_forward, lasp/lasp_fuse.py:356-406 */
+/* the whole forward: lasp_forward, lasp/lasp_fuse.py:356-406.  On the tensor-core path ONE launch (span
+ * totals, the states at the span borders from them and kv_in, the walk; kv_out on the way) whenever the
+ * spans fit one per SM; otherwise, and on the fp32 path, the three phases back to back. */
 LASP_B200_API int lasp_b200_forward(const lasp_problem* p, const lasp_fwd_args* a, void* stream);
 
 /* ---- backward phases ------------------------------------------------- */
@@ -153,8 +155,15 @@ LASP_B200_API int lasp_b200_bwd_scan(const lasp_problem* p, const lasp_bwd_args*
  * lasp/lasp_fuse_parallel.py:339-519,665-830 (== _bwd_intra_kernel +
  * _bwd_inter_kernel, lasp/lightning_attention.py:86-393). */
 LASP_B200_API int lasp_b200_bwd_grads(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
-/* the three phases back to back: lasp_backward, lasp/lasp_fuse.py:409-475 */
+/* the whole backward: lasp_backward, lasp/lasp_fuse.py:409-475.  On the tensor-core path two launches:
+ * dQ (a forward walk over the states the forward pass kept in fwd_ws) and dK,dV (one fused launch: span
+ * totals of q,do, the suffix states from them and dkv_in, the reverse walk; dkv_out on the way). */
 LASP_B200_API int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
+/* those two launches on their own (each independent of the other's results); on the fp32 path the
+ * first does nothing and the second is the whole backward.  Replace _bwd_inter_kernel's forward sweep
+ * and reverse sweep, lasp/lightning_attention.py:238-278 and :333-393, with their intra-block parts. */
+LASP_B200_API int lasp_b200_bwd_dq(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
+LASP_B200_API int lasp_b200_bwd_dkv(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
 
 /* x_out = exp(-s_h n) x_in + x_local on (b,h,d,e) fp32 states; x_in may be NULL.
  * Replaces the torch glue KV = block_decay*KV + kv, lasp/lasp_naive.py:565,614. */

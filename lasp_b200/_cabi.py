@@ -74,6 +74,8 @@ SIGNATURES = {
     "lasp_b200_bwd_scan": (C.c_int, [_PP, _BP, C.c_void_p]),
     "lasp_b200_bwd_grads": (C.c_int, [_PP, _BP, C.c_void_p]),
     "lasp_b200_backward": (C.c_int, [_PP, _BP, C.c_void_p]),
+    "lasp_b200_bwd_dq": (C.c_int, [_PP, _BP, C.c_void_p]),
+    "lasp_b200_bwd_dkv": (C.c_int, [_PP, _BP, C.c_void_p]),
     "lasp_b200_state_combine": (C.c_int, [C.c_int] * 5 + [C.c_void_p] * 5),
     "lasp_b200_read_status": (C.c_int, [C.POINTER(C.c_int32), C.c_int, C.c_void_p]),
     "lasp_b200_copy_status_async": (C.c_int, [C.c_void_p, C.c_void_p]),

@@ -289,6 +289,26 @@ int lasp_b200_bwd_grads(const lasp_problem* p, const lasp_bwd_args* a, void* str
   return st != LASP_OK ? st : bwd_grads(m, a, static_cast<cudaStream_t>(stream));
 }
 
+// The two launches of the tensor-core backward, separately (the fp32 path has one gradient kernel: there
+// lasp_b200_bwd_dq does nothing and lasp_b200_bwd_dkv is the whole backward).
+int lasp_b200_bwd_dq(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
+  lasp::Dims m;
+  int st = check_bwd(p, a, &m, true);
+  if (st != LASP_OK || !m.walk) return st;
+  return cuda_fail(lasp::walk_bwd_dq(m, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m), a->dq,
+                                     static_cast<cudaStream_t>(stream)));
+}
+
+int lasp_b200_bwd_dkv(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
+  lasp::Dims m;
+  int st = check_bwd(p, a, &m, true);
+  if (st != LASP_OK) return st;
+  if (!fusable(m)) return lasp_b200_backward(p, a, stream);
+  return cuda_fail(lasp::walk_bwd_dkv_fused(m, a->q, a->k, a->v, a->d_o, a->s, a->dkv_in, a->dkv_out,
+                                            lasp::ws_walk_sync(a->ws), lasp::ws_walk_totals(a->ws), a->dk, a->dv,
+                                            static_cast<cudaStream_t>(stream)));
+}
+
 int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_bwd(p, a, &m, true);

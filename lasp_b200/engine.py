@@ -188,6 +188,12 @@ class Backward:
     def grads(self):
         self._call("lasp_b200_bwd_grads")
 
+    def dq_only(self):
+        self._call("lasp_b200_bwd_dq")
+
+    def dkv_only(self):
+        self._call("lasp_b200_bwd_dkv")
+
     def run(self):
         self._call("lasp_b200_backward")
         return self.dq, self.dk, self.dv
