@@ -164,6 +164,9 @@ LASP_B200_API int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args*
  * and reverse sweep, lasp/lightning_attention.py:238-278 and :333-393, with their intra-block parts. */
 LASP_B200_API int lasp_b200_bwd_dq(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
 LASP_B200_API int lasp_b200_bwd_dkv(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
+/* dK, dV alone from the suffix states that lasp_b200_bwd_scan (or lasp_b200_exchange_scan) left in ws:
+ * lasp_b200_bwd_grads without its dQ launch (on the fp32 path: all of lasp_b200_bwd_grads). */
+LASP_B200_API int lasp_b200_bwd_dkv_walk(const lasp_problem* p, const lasp_bwd_args* a, void* stream);
 
 /* x_out = exp(-s_h n) x_in + x_local on (b,h,d,e) fp32 states; x_in may be NULL.
  * Replaces the torch glue KV = block_decay*KV + kv, lasp/lasp_naive.py:565,614. */
@@ -203,11 +206,15 @@ LASP_B200_API int lasp_b200_state_combine(int b, int h, int d, int e, int n, con
  * Waits give up after wait_clocks GPU clocks (0 = about ten seconds), set bit 4
  * of the fault word (lasp_b200_read_status) and make the states they could not
  * complete NaN, so that a late peer cannot pass for a delivered state. */
+/* The two halves can also go out as two launches of the same step - LASP_EXCHANGE_PUSH as soon as the
+ * chunk states exist, LASP_EXCHANGE_GATHER (which completes the step) later - so that work that does not
+ * need the incoming state (dQ in the backward pass) runs between them while the states are in flight. */
+typedef enum { LASP_EXCHANGE_BOTH = 0, LASP_EXCHANGE_PUSH = 1, LASP_EXCHANGE_GATHER = 2 } lasp_exchange_phase;
 typedef struct {
   int32_t ranks;             /* group size, 2..8 */
   int32_t position;          /* this rank's place in the chain order */
   int32_t reverse;           /* 0: forward (KV, prefix scan); 1: backward (dKV, suffix scan) */
-  int32_t reserved;
+  int32_t phase;             /* lasp_exchange_phase */
   const float* s;            /* h decay rates */
   void* ws;                  /* the forward / backward workspace after its chunk-state phase */
   size_t ws_bytes;

@@ -15,6 +15,7 @@ ABI_VERSION = 2
 # lasp_dtype / lasp_path / lasp_status of include/lasp_b200.h
 F32, BF16, F16 = 0, 1, 2
 PATH_AUTO, PATH_SIMT, PATH_TENSOR = 0, 1, 2
+EXCHANGE_BOTH, EXCHANGE_PUSH, EXCHANGE_GATHER = 0, 1, 2
 OK = 0
 
 
@@ -49,7 +50,7 @@ class BwdArgs(C.Structure):
 
 
 class ExchangeArgs(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in ("ranks", "position", "reverse", "reserved")] + \
+    _fields_ = [(n, C.c_int32) for n in ("ranks", "position", "reverse", "phase")] + \
                [("s", C.c_void_p), ("ws", C.c_void_p), ("ws_bytes", C.c_size_t)] + \
                [(n, C.c_void_p) for n in ("my_slots", "my_acks", "counters")] + \
                [("peer_slots", C.c_void_p * 8), ("peer_acks", C.c_void_p * 8), ("wait_clocks", C.c_int64)]
@@ -76,6 +77,7 @@ SIGNATURES = {
     "lasp_b200_backward": (C.c_int, [_PP, _BP, C.c_void_p]),
     "lasp_b200_bwd_dq": (C.c_int, [_PP, _BP, C.c_void_p]),
     "lasp_b200_bwd_dkv": (C.c_int, [_PP, _BP, C.c_void_p]),
+    "lasp_b200_bwd_dkv_walk": (C.c_int, [_PP, _BP, C.c_void_p]),
     "lasp_b200_state_combine": (C.c_int, [C.c_int] * 5 + [C.c_void_p] * 5),
     "lasp_b200_read_status": (C.c_int, [C.POINTER(C.c_int32), C.c_int, C.c_void_p]),
     "lasp_b200_copy_status_async": (C.c_int, [C.c_void_p, C.c_void_p]),

@@ -176,8 +176,11 @@ class SequenceParallelAttention(torch.autograd.Function):
         if ctx.exchange is not None:
             bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws)
             bw.chunk_states()
-            ctx.exchange.exchange_scan(ctx.plan, bw.ws, s, backward=True)
-            bw.grads()
+            # dQ needs no incoming state: it runs between the two halves of the hand-over
+            ctx.exchange.exchange_scan(ctx.plan, bw.ws, s, backward=True, phase="push")
+            bw.dq_only()
+            ctx.exchange.exchange_scan(ctx.plan, bw.ws, s, backward=True, phase="gather")
+            bw.dkv_after_scan()
             ENGINE.fault_watch(q.device).arm(q.device)   # looked at when the next call starts
             return bw.dq, bw.dk, bw.dv, None, None, None, None
         bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws, dkv_in=dkv_in,

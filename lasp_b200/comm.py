@@ -117,10 +117,12 @@ class NvlinkExchange:
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)   # every rank has zeroed its flags before any peer writes one
 
-    def exchange_scan(self, plan, ws, s, backward: bool, wait_clocks: int | None = None) -> None:
+    def exchange_scan(self, plan, ws, s, backward: bool, wait_clocks: int | None = None, phase: str = "both") -> None:
         """Launch the hand-over of one direction on the current stream, between the chunk-state phase and
         the output / gradient phase of the call that owns ``ws`` and in place of its scan phase.
-        Forward: states flow towards higher ranks; backward: towards lower ranks."""
+        Forward: states flow towards higher ranks; backward: towards lower ranks.  ``phase``: "both", or
+        "push" followed later by "gather" (two launches of one step; whatever runs between them overlaps
+        the states' flight)."""
         from . import _cabi, engine
         assert plan.b * plan.h * plan.d * plan.e == self.elems
         pos = self.size - 1 - self.rank if backward else self.rank
@@ -128,6 +130,7 @@ class NvlinkExchange:
         sl = s.reshape(-1).to(device=ws.device, dtype=torch.float32).contiguous()
         a = _cabi.ExchangeArgs()
         a.ranks, a.position, a.reverse = self.size, pos, 1 if backward else 0
+        a.phase = {"both": _cabi.EXCHANGE_BOTH, "push": _cabi.EXCHANGE_PUSH, "gather": _cabi.EXCHANGE_GATHER}[phase]
         a.s, a.ws, a.ws_bytes = sl.data_ptr(), ws.data_ptr(), ws.numel()
         me = self.ptrs[self.rank] + off
         a.my_acks, a.counters, a.my_slots = me, me + 8192, me + self._HEADER

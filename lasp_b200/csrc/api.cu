@@ -299,6 +299,16 @@ int lasp_b200_bwd_dq(const lasp_problem* p, const lasp_bwd_args* a, void* stream
                                      static_cast<cudaStream_t>(stream)));
 }
 
+int lasp_b200_bwd_dkv_walk(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
+  lasp::Dims m;
+  int st = check_bwd(p, a, &m, true);
+  if (st != LASP_OK) return st;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (!m.walk) return bwd_grads(m, a, cs);
+  return cuda_fail(lasp::walk_bwd_dkv(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->ws, m), a->dk, a->dv,
+                                      cs));
+}
+
 int lasp_b200_bwd_dkv(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
   lasp::Dims m;
   int st = check_bwd(p, a, &m, true);
@@ -342,6 +352,7 @@ int lasp_b200_exchange_scan(const lasp_problem* p, const lasp_exchange_args* a, 
   if (st != LASP_OK) return st;
   if (!a || !a->s || !a->ws || !a->counters) return LASP_ERR_NULL;
   if (a->ranks < 2 || a->ranks > 8 || a->position < 0 || a->position >= a->ranks) return LASP_ERR_SHAPE;
+  if (a->phase < LASP_EXCHANGE_BOTH || a->phase > LASP_EXCHANGE_GATHER) return LASP_ERR_SHAPE;
   if ((m.d * m.e) % 4) return LASP_ERR_SHAPE;
   if (a->position > 0 && !a->my_slots) return LASP_ERR_NULL;
   if (a->position < a->ranks - 1 && !a->my_acks) return LASP_ERR_NULL;

@@ -73,6 +73,8 @@ struct ExchangeParams {
   int n_dst;                    // destinations = positions me+1..me+n_dst
   int ranks;                    // group size (slot stride)
   int h, de, n, nc, chunk, reverse;
+  int n_push;                   // push CTAs of this launch (0: the launch only gathers and scans)
+  int gathers;                  // 1: the launch has the gather + scan CTAs and completes the step
   long long elems;
   long long wait_clocks;
 };
@@ -108,7 +110,7 @@ __device__ __forceinline__ float4 local_total(const ExchangeParams& p, long long
 __global__ void __launch_bounds__(256) k_exchange_scan(const ExchangeParams p) {
   const uint32_t step = p.counters[0] + 1;
   const int parity = step & 1;
-  const int n_push = push_ctas(p.n_dst);
+  const int n_push = p.n_push;
   const int last_len = p.n - (p.nc - 1) * p.chunk;
   if ((int)blockIdx.x < n_push) {
     // ---- push: my total -> slot [parity][me] of one destination, one slice part
@@ -212,7 +214,8 @@ __global__ void __launch_bounds__(256) k_exchange_scan(const ExchangeParams p) {
       }
     }
   }
-  if (threadIdx.x == 0) {
+  // the launch that gathers completes the step (a push-only launch ahead of it belongs to the same step)
+  if (threadIdx.x == 0 && p.gathers) {
     __threadfence();
     if (atomicAdd(&p.counters[1], 1u) == (uint32_t)(gridDim.x - 1)) {
       p.counters[1] = 0;
@@ -252,7 +255,10 @@ cudaError_t exchange_scan(const Dims& m, const lasp_exchange_args& a, const floa
   p.elems = (long long)m.b * m.h * m.d * m.e;
   p.wait_clocks = a.wait_clocks > 0 ? a.wait_clocks : 20000000000LL;  // about ten seconds
   p.push_parts = push_parts(p.n_dst);
-  const int ctas = push_ctas(p.n_dst) + kSlices * kGatherCtas;
+  p.n_push = (a.phase == LASP_EXCHANGE_GATHER) ? 0 : push_ctas(p.n_dst);
+  p.gathers = a.phase != LASP_EXCHANGE_PUSH;
+  const int ctas = p.n_push + (p.gathers ? kSlices * kGatherCtas : 0);
+  if (ctas == 0) return cudaSuccess;   // a push-only launch of the rank that has nobody after it
   k_exchange_scan<<<ctas, 256, 0, st>>>(p);
   return cudaGetLastError();
 }

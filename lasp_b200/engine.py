@@ -194,6 +194,9 @@ class Backward:
     def dkv_only(self):
         self._call("lasp_b200_bwd_dkv")
 
+    def dkv_after_scan(self):
+        self._call("lasp_b200_bwd_dkv_walk")
+
     def run(self):
         self._call("lasp_b200_backward")
         return self.dq, self.dk, self.dv

@@ -37,7 +37,7 @@ class FixedStep:
         tensor = self.plan.path_name == "tensor"
         if self.relay is None:
             return 3 if tensor else 6
-        return 7 if tensor else 6
+        return 8 if tensor else 7
 
     @property
     def outputs(self):
@@ -53,5 +53,7 @@ class FixedStep:
         self.relay.exchange_scan(self.plan, fw.ws, self.s, backward=False)
         fw.output()
         bw.chunk_states()
-        self.relay.exchange_scan(self.plan, bw.ws, self.s, backward=True)
-        bw.grads()
+        self.relay.exchange_scan(self.plan, bw.ws, self.s, backward=True, phase="push")
+        bw.dq_only()                       # needs no incoming state: overlaps the states' flight
+        self.relay.exchange_scan(self.plan, bw.ws, self.s, backward=True, phase="gather")
+        bw.dkv_after_scan()
