@@ -227,6 +227,23 @@ typedef struct {
 } lasp_exchange_args;
 LASP_B200_API int lasp_b200_exchange_scan(const lasp_problem* p, const lasp_exchange_args* a, void* stream);
 
+/* Compute and hand-over in ONE launch per direction: the fused forward kernel (lasp_b200_forward) and
+ * the fused dK,dV kernel (lasp_b200_bwd_dkv) with the group's peer-mapped buffers (x: ranks, position,
+ * my_slots, my_acks, counters, peer_slots, peer_acks, wait_clocks; for the backward call the chain order
+ * reversed; the other fields are ignored).  The CTA that owns the end of a sequence stores the
+ * sequence's total into the slots of the ranks after this one as soon as the span totals exist; every
+ * CTA adds what the ranks before stored here to the state at its span's border, and walks.  kv_in /
+ * kv_out (dkv_in / dkv_out) of the arguments are not used.  Replaces, for a sequence-parallel rank,
+ * LaspFuseParallel.forward / .backward of lasp/lasp_fuse_parallel.py:1075-1137 in one launch each
+ * (plus lasp_b200_bwd_dq).  Needs every span on an SM of its own: lasp_b200_linked_ok returns 1 when
+ * the problem qualifies (0: use the chunk-state phase, lasp_b200_exchange_scan and the output phase),
+ * and the calls return LASP_ERR_PATH when it does not. */
+LASP_B200_API int lasp_b200_linked_ok(const lasp_problem* p);
+LASP_B200_API int lasp_b200_forward_linked(const lasp_problem* p, const lasp_fwd_args* a, const lasp_exchange_args* x,
+                                           void* stream);
+LASP_B200_API int lasp_b200_bwd_dkv_linked(const lasp_problem* p, const lasp_bwd_args* a, const lasp_exchange_args* x,
+                                           void* stream);
+
 /* Copies this device's sticky kernel-fault word to *status_host (synchronises
  * the stream) and clears it when clear != 0.  0 = no kernel reported a fault;
  * the tensor-core kernels set bits when one of their bounded waits (TMA

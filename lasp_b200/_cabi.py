@@ -83,6 +83,9 @@ SIGNATURES = {
     "lasp_b200_copy_status_async": (C.c_int, [C.c_void_p, C.c_void_p]),
     "lasp_b200_forward_static": (C.c_int, [_PP, _FP, C.c_void_p]),
     "lasp_b200_exchange_scan": (C.c_int, [_PP, C.POINTER(ExchangeArgs), C.c_void_p]),
+    "lasp_b200_linked_ok": (C.c_int, [_PP]),
+    "lasp_b200_forward_linked": (C.c_int, [_PP, _FP, C.POINTER(ExchangeArgs), C.c_void_p]),
+    "lasp_b200_bwd_dkv_linked": (C.c_int, [_PP, _BP, C.POINTER(ExchangeArgs), C.c_void_p]),
 }
 STATIC_SCRATCH_BYTES = 64 << 20  # LASP_B200_STATIC_SCRATCH_BYTES
 

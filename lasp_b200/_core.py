@@ -142,9 +142,12 @@ class SequenceParallelAttention(torch.autograd.Function):
         if exchange is not None:
             ENGINE.fault_watch(q.device).poll()          # a fault of the previous step surfaces here
             fw = ENGINE.Forward(plan, q, k, v, s)
-            fw.chunk_states()
-            exchange.exchange_scan(plan, fw.ws, s, backward=False)
-            fw.output()
+            if ENGINE.linked_ok(plan):
+                fw.run_linked(exchange.link_args(backward=False))     # compute and hand-over in one launch
+            else:
+                fw.chunk_states()
+                exchange.exchange_scan(plan, fw.ws, s, backward=False)
+                fw.output()
         else:
             fw = ENGINE.Forward(plan, q, k, v, s, kv_in=kv_in, kv_out=KV if rank < last else None)
             if overlap:
@@ -175,12 +178,22 @@ class SequenceParallelAttention(torch.autograd.Function):
         dkv_in = DKV if rank < last else None
         if ctx.exchange is not None:
             bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws)
-            bw.chunk_states()
-            # dQ needs no incoming state: it runs between the two halves of the hand-over
-            ctx.exchange.exchange_scan(ctx.plan, bw.ws, s, backward=True, phase="push")
-            bw.dq_only()
-            ctx.exchange.exchange_scan(ctx.plan, bw.ws, s, backward=True, phase="gather")
-            bw.dkv_after_scan()
+            if ENGINE.linked_ok(ctx.plan):
+                # dQ needs no incoming state.  The last rank has nobody to wait for and the others wait for
+                # it: it sends first; the others do their dQ while the states travel.
+                if rank == last:
+                    bw.dkv_linked(ctx.exchange.link_args(backward=True))
+                    bw.dq_only()
+                else:
+                    bw.dq_only()
+                    bw.dkv_linked(ctx.exchange.link_args(backward=True))
+            else:
+                bw.chunk_states()
+                # dQ needs no incoming state: it runs between the two halves of the hand-over
+                ctx.exchange.exchange_scan(ctx.plan, bw.ws, s, backward=True, phase="push")
+                bw.dq_only()
+                ctx.exchange.exchange_scan(ctx.plan, bw.ws, s, backward=True, phase="gather")
+                bw.dkv_after_scan()
             ENGINE.fault_watch(q.device).arm(q.device)   # looked at when the next call starts
             return bw.dq, bw.dk, bw.dv, None, None, None, None
         bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws, dkv_in=dkv_in,

@@ -117,6 +117,21 @@ class NvlinkExchange:
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)   # every rank has zeroed its flags before any peer writes one
 
+    def link_args(self, backward: bool, wait_clocks: int | None = None):
+        """The group's buffers of one direction as the ``lasp_exchange_args`` the linked calls take."""
+        from . import _cabi
+        pos = self.size - 1 - self.rank if backward else self.rank
+        off = self.region if backward else 0
+        a = _cabi.ExchangeArgs()
+        a.ranks, a.position, a.reverse = self.size, pos, 1 if backward else 0
+        me = self.ptrs[self.rank] + off
+        a.my_acks, a.counters, a.my_slots = me, me + 8192, me + self._HEADER
+        for q in range(self.size):
+            base = self.ptrs[self.size - 1 - q if backward else q] + off   # buffer of the rank at position q
+            a.peer_acks[q], a.peer_slots[q] = base, base + self._HEADER
+        a.wait_clocks = wait_timeout_clocks() if wait_clocks is None else wait_clocks
+        return a
+
     def exchange_scan(self, plan, ws, s, backward: bool, wait_clocks: int | None = None, phase: str = "both") -> None:
         """Launch the hand-over of one direction on the current stream, between the chunk-state phase and
         the output / gradient phase of the call that owns ``ws`` and in place of its scan phase.

@@ -264,7 +264,8 @@ int lasp_b200_forward(const lasp_problem* p, const lasp_fwd_args* a, void* strea
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (fusable(m))
     return cuda_fail(lasp::walk_fwd_fused(m, a->q, a->k, a->v, a->s, a->kv_in, a->kv_out, lasp::ws_walk_sync(a->ws),
-                                          lasp::ws_walk_totals(a->ws), lasp::ws_walk_border(a->ws, m), a->o, cs));
+                                          lasp::ws_walk_totals(a->ws), lasp::ws_walk_border(a->ws, m), a->o, nullptr,
+                                          cs));
   if ((st = fwd_chunk_states(m, a, cs)) != LASP_OK) return st;
   if ((st = fwd_scan(m, a, cs)) != LASP_OK) return st;
   return fwd_output(m, a, cs);
@@ -316,7 +317,7 @@ int lasp_b200_bwd_dkv(const lasp_problem* p, const lasp_bwd_args* a, void* strea
   if (!fusable(m)) return lasp_b200_backward(p, a, stream);
   return cuda_fail(lasp::walk_bwd_dkv_fused(m, a->q, a->k, a->v, a->d_o, a->s, a->dkv_in, a->dkv_out,
                                             lasp::ws_walk_sync(a->ws), lasp::ws_walk_totals(a->ws), a->dk, a->dv,
-                                            static_cast<cudaStream_t>(stream)));
+                                            nullptr, static_cast<cudaStream_t>(stream)));
 }
 
 int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stream) {
@@ -331,7 +332,7 @@ int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stre
       return st;
     return cuda_fail(lasp::walk_bwd_dkv_fused(m, a->q, a->k, a->v, a->d_o, a->s, a->dkv_in, a->dkv_out,
                                               lasp::ws_walk_sync(a->ws), lasp::ws_walk_totals(a->ws), a->dk, a->dv,
-                                              cs));
+                                              nullptr, cs));
   }
   if ((st = bwd_chunk_states(m, a, cs)) != LASP_OK) return st;
   if ((st = bwd_scan(m, a, cs)) != LASP_OK) return st;
@@ -344,6 +345,51 @@ int lasp_b200_state_combine(int b, int h, int d, int e, int n, const float* s, c
   if (b <= 0 || h <= 0 || d <= 0 || e <= 0 || n < 0 || (d * e) % 4 || (long long)b * h > 65535) return LASP_ERR_SHAPE;
   if (!aligned16(x_in) || !aligned16(x_local) || !aligned16(x_out)) return LASP_ERR_ALIGN;
   return cuda_fail(lasp::state_combine(b, h, d, e, n, s, x_in, x_local, x_out, static_cast<cudaStream_t>(stream)));
+}
+
+// checks of the peer-mapped buffers shared by the hand-over entry points
+static int check_link(const lasp_exchange_args* a) {
+  if (!a || !a->counters) return LASP_ERR_NULL;
+  if (a->ranks < 2 || a->ranks > 8 || a->position < 0 || a->position >= a->ranks) return LASP_ERR_SHAPE;
+  if (a->position > 0 && !a->my_slots) return LASP_ERR_NULL;
+  if (a->position < a->ranks - 1 && !a->my_acks) return LASP_ERR_NULL;
+  for (int q = 0; q < a->ranks; ++q) {
+    if (q < a->position && !a->peer_acks[q]) return LASP_ERR_NULL;
+    if (q > a->position && !a->peer_slots[q]) return LASP_ERR_NULL;
+  }
+  if (!aligned16(a->my_slots)) return LASP_ERR_ALIGN;
+  return LASP_OK;
+}
+
+int lasp_b200_linked_ok(const lasp_problem* p) {
+  lasp::Dims m;
+  int st = make_dims(p, &m);
+  if (st != LASP_OK) return st;
+  return (m.walk && !unfused_requested() && m.b * m.h * m.nc <= lasp::sm_count()) ? 1 : 0;
+}
+
+int lasp_b200_forward_linked(const lasp_problem* p, const lasp_fwd_args* a, const lasp_exchange_args* x,
+                             void* stream) {
+  lasp::Dims m;
+  int st = check_fwd(p, a, &m, true);
+  if (st != LASP_OK) return st;
+  if ((st = check_link(x)) != LASP_OK) return st;
+  if (lasp_b200_linked_ok(p) != 1) return LASP_ERR_PATH;
+  return cuda_fail(lasp::walk_fwd_fused(m, a->q, a->k, a->v, a->s, nullptr, nullptr, lasp::ws_walk_sync(a->ws),
+                                        lasp::ws_walk_totals(a->ws), lasp::ws_walk_border(a->ws, m), a->o, x,
+                                        static_cast<cudaStream_t>(stream)));
+}
+
+int lasp_b200_bwd_dkv_linked(const lasp_problem* p, const lasp_bwd_args* a, const lasp_exchange_args* x,
+                             void* stream) {
+  lasp::Dims m;
+  int st = check_bwd(p, a, &m, true);
+  if (st != LASP_OK) return st;
+  if ((st = check_link(x)) != LASP_OK) return st;
+  if (lasp_b200_linked_ok(p) != 1) return LASP_ERR_PATH;
+  return cuda_fail(lasp::walk_bwd_dkv_fused(m, a->q, a->k, a->v, a->d_o, a->s, nullptr, nullptr,
+                                            lasp::ws_walk_sync(a->ws), lasp::ws_walk_totals(a->ws), a->dk, a->dv, x,
+                                            static_cast<cudaStream_t>(stream)));
 }
 
 int lasp_b200_exchange_scan(const lasp_problem* p, const lasp_exchange_args* a, void* stream) {

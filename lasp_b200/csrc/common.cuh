@@ -111,13 +111,13 @@ cudaError_t walk_fwd_output(const Dims& m, const void* q, const void* k, const v
                             const float* prefix, void* o, cudaStream_t st);
 cudaError_t walk_fwd_fused(const Dims& m, const void* q, const void* k, const void* v, const float* s,
                            const float* x_in, float* x_out, uint32_t* sync, float* totals, float* prefix, void* o,
-                           cudaStream_t st);
+                           const lasp_exchange_args* link, cudaStream_t st);
 cudaError_t walk_bwd_dq(const Dims& m, const void* k, const void* v, const void* d_o, const float* s,
                         const float* prefix, void* dq, cudaStream_t st);
 cudaError_t walk_bwd_dkv(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
                          const float* s, const float* suffix, void* dk, void* dv, cudaStream_t st);
 cudaError_t walk_bwd_dkv_fused(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
                                const float* s, const float* x_in, float* x_out, uint32_t* sync, float* totals,
-                               void* dk, void* dv, cudaStream_t st);
+                               void* dk, void* dv, const lasp_exchange_args* link, cudaStream_t st);
 
 }  // namespace lasp

@@ -20,6 +20,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include "exchange_layout.h"
 #include "tc_common.cuh"
 
 namespace lasp {
@@ -217,6 +218,116 @@ __device__ __forceinline__ bool wait_flag_eq(const uint32_t* flag, uint32_t want
   return true;
 }
 
+// The peer-mapped buffers of a sequence-parallel group for one direction (word format, slots and
+// acknowledgements as in relay_kernels.cu).  With a link the fused kernels hand the rank state over
+// themselves: the CTA that owns the last span of a sequence (in walk order) stores the sequence's total
+// into the slots of the ranks after this one as soon as the span totals exist, and every CTA adds what
+// the ranks before stored here to its border state - one launch per direction computes AND exchanges.
+struct Link {
+  const uint2* my_slots;                 // local: slots[parity][source][element] of {value, step} words
+  uint2* dst_slots[xl::kMaxRanks];       // peer: each destination's slots
+  uint32_t* src_acks[xl::kMaxRanks];     // peer: acknowledgement words in each source's memory
+  const uint32_t* my_acks;               // local acknowledgement words [destination]
+  uint32_t* counters;                    // local: [0] = last completed step
+  int ranks;                             // group size; 0 = no link
+  int me;                                // this rank's place in the chain order
+  long long wait_clocks;
+};
+
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_volatile_v4(void* p, uint4 v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// This thread's part (row `row`, columns [col0, col0 + N)) of a sequence's outgoing total, dec * P + own,
+// stored as {value, step} words into the slots of every rank after this one that it still reaches.  The
+// words of a sequence are in lane order like the states themselves, so sender and receiver are coalesced.
+template <int N, int ROWS>
+__device__ __forceinline__ void link_send(const Link& l, uint32_t step, long long elems, size_t seq_off, int row,
+                                          int col0, float dec, const float (&P)[N], const float* own, float sn) {
+  const float4* src = reinterpret_cast<const float4*>(own) + (size_t)(col0 / 4) * ROWS + row;
+  const int n_dst = l.ranks - 1 - l.me;
+#pragma unroll 4
+  for (int q = 0; q < N / 4; ++q) {
+    const float4 o = __ldcg(src + (size_t)q * ROWS);
+    const float4 t = make_float4(fmaf(dec, P[4 * q], o.x), fmaf(dec, P[4 * q + 1], o.y), fmaf(dec, P[4 * q + 2], o.z),
+                                 fmaf(dec, P[4 * q + 3], o.w));
+    const size_t word = seq_off + ((size_t)(col0 / 4 + q) * ROWS + row) * 4;
+    for (int di = 0; di < n_dst; ++di) {
+      if (!xl::reaches(sn, di)) break;   // farther ranks are out of reach too
+      uint2* out = l.dst_slots[l.me + 1 + di] + xl::slot_offset(step & 1, l.ranks, l.me, elems) + word;
+      st_volatile_v4(out, make_uint4(__float_as_uint(t.x), step, __float_as_uint(t.y), step));
+      st_volatile_v4(out + 2, make_uint4(__float_as_uint(t.z), step, __float_as_uint(t.w), step));
+    }
+  }
+}
+
+// P += dec * sum over the ranks before this one of exp(-sn)^(hops) * their total of this sequence, each word
+// awaited until it carries `step`.  Returns false when a wait ran out (P is then NaN).
+template <int N, int ROWS>
+__device__ __forceinline__ bool link_receive(const Link& l, uint32_t step, long long elems, size_t seq_off, int row,
+                                             int col0, float dec, float (&P)[N], float sn) {
+  bool late = false;
+  for (int src = l.me - 1; src >= 0; --src) {
+    const int hops = l.me - 1 - src;
+    if (!xl::reaches(sn, hops)) break;   // farther ranks are out of reach too
+    const float wgt = dec * expf(-sn * (float)hops);
+    const uint2* in = l.my_slots + xl::slot_offset(step & 1, l.ranks, src, elems) + seq_off;
+    constexpr int kBatch = 4;   // float4 chunks in flight
+#pragma unroll
+    for (int q0 = 0; q0 < N / 4; q0 += kBatch) {
+      uint4 w0[kBatch], w1[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const uint2* p = in + ((size_t)(col0 / 4 + q0 + u) * ROWS + row) * 4;
+        w0[u] = ld_volatile_v4(p);
+        w1[u] = ld_volatile_v4(p + 2);
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        if (!late && (w0[u].y != step || w0[u].w != step || w1[u].y != step || w1[u].w != step)) {
+          const uint2* p = in + ((size_t)(col0 / 4 + q0 + u) * ROWS + row) * 4;
+          const long long t0 = clock64();   // after one wait has run out this thread waits no more
+          do {
+            w0[u] = ld_volatile_v4(p);
+            w1[u] = ld_volatile_v4(p + 2);
+            if (clock64() - t0 > l.wait_clocks) {
+              late = true;
+              break;
+            }
+          } while (w0[u].y != step || w0[u].w != step || w1[u].y != step || w1[u].w != step);
+        }
+        const int j = 4 * (q0 + u);
+        P[j] = fmaf(wgt, __uint_as_float(w0[u].x), P[j]);
+        P[j + 1] = fmaf(wgt, __uint_as_float(w0[u].z), P[j + 1]);
+        P[j + 2] = fmaf(wgt, __uint_as_float(w1[u].x), P[j + 2]);
+        P[j + 3] = fmaf(wgt, __uint_as_float(w1[u].z), P[j + 3]);
+      }
+    }
+  }
+  if (late) {   // a state that did not arrive must not look like one that did
+#pragma unroll
+    for (int j = 0; j < N; ++j) P[j] = __int_as_float(0x7fc00000);
+  }
+  return !late;
+}
+
+// spins until *flag >= want (as a step number) or `limit` clocks pass
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, long long limit) {
+  if ((int32_t)(ld_volatile_u32(flag) - want) >= 0) return true;
+  const long long t0 = clock64();
+  while ((int32_t)(ld_volatile_u32(flag) - want) < 0) {
+    if (clock64() - t0 > limit) return false;
+  }
+  return true;
+}
+
 struct WalkArgs {
   const float* s;
   const float* p0;     // not fused: fp32 state of every span at its border, [items][D][E] (from the scan)
@@ -227,8 +338,11 @@ struct WalkArgs {
   float* x_out;        // fused: outgoing rank state (b,h,d,e) or NULL
   int h, n, tiles, span, nspans, items;
   int all_totals;      // fused: the last span of a sequence computes its total too
+  int coop;            // fused: every CTA has exactly one span and the CTAs synchronise (several spans per
+                       // sequence, or a link)
   long long wait_clocks;
   int32_t* fault;
+  Link link;           // fused: hand the rank state over inside the launch (link.ranks > 0)
 };
 constexpr int kSyncFlags = 32;
 
@@ -288,7 +402,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
   __shared__ uint64_t x_full[2], y_full[2], z_full[2], s_full[2], sm_ready[2], o_full[2], o2_full[2], staged[2];
   __shared__ uint64_t p_ready, l_free, o_free, ys_ready, o2s_ready, l_full;
   __shared__ uint64_t ring_full[2], ring_scaled[2], ring_empty[2], sum_done;   // the span-total phase
-  __shared__ uint32_t tmem_slot, step_s;
+  __shared__ uint32_t tmem_slot, step_s, step_x;
   __shared__ int dead;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int32_t* fault = a.fault;
@@ -319,7 +433,10 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
     prefetch_tensormap(&map_y);
     prefetch_tensormap(&map_z);
     prefetch_tensormap(&map_out);
-    if constexpr (FUSED) step_s = a.nspans > 1 ? ld_volatile_u32(a.sync) + 1 : 0;
+    if constexpr (FUSED) {
+      step_s = a.coop ? ld_volatile_u32(a.sync) + 1 : 0;                       // this launch among those on the workspace
+      step_x = a.link.ranks > 0 ? ld_volatile_u32(a.link.counters) + 1 : 0;    // this hand-over in the group
+    }
   }
   if (warp == 2) tmem_alloc(&tmem_slot, 512);
   tc_fence_before_sync();
@@ -334,7 +451,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
   bool sums = false;
   int sum_t0 = 0, sum_t1 = 0, my_bh = 0, my_sp = 0;
   if constexpr (FUSED) {
-    if (a.nspans > 1 && w.start(blockIdx.x, gridDim.x)) {
+    if (a.coop && w.start(blockIdx.x, gridDim.x)) {
       my_bh = w.bh;
       my_sp = w.it - w.bh * a.nspans;
       sum_t0 = w.t0;
@@ -580,6 +697,34 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
               fma_state<kHalfE, D>(a.totals + (size_t)(w.bh * a.nspans + j) * D * E, row, half * kHalfE,
                                    decay_pow(sl2, (sp_idx - 1 - j) * a.span * C), P);
           }
+          if (a.link.ranks > 0) {
+            // hand-over of the rank state inside the launch.  P holds the local part of the border state.
+            const float sn = a.s[w.bh % a.h] * (float)a.n;
+            const long long elems = (long long)(a.items / a.nspans) * D * E;
+            const size_t seq_off = (size_t)w.bh * D * E;
+            const int n_dst = a.link.ranks - 1 - a.link.me;
+            if (sp_idx == a.nspans - 1 && n_dst > 0) {
+              // this CTA owns the end of the sequence: the sequence's total, lambda^(n - start) P + T, goes to
+              // the ranks after this one (whose readers acknowledged the slot's previous use)
+              if (xl::needs_ack_wait(step_x) && tid - 64 < n_dst && !dead) {
+                if (!wait_flag_ge(a.link.my_acks + xl::ack_index(a.link.me + 1 + (tid - 64), 0), step_x - 2,
+                                  a.link.wait_clocks)) {
+                  dead = 1;
+                  atomicOr(fault, kFaultRelayWait);
+                }
+              }
+              named_sync(1, kWorkers);
+              if (row < D)
+                link_send<kHalfE, D>(a.link, step_x, elems, seq_off, row, half * kHalfE,
+                                     decay_pow(sl2, a.n - w.t0 * C), P, a.totals + (size_t)w.it * D * E, sn);
+            }
+            if (a.link.me > 0 && row < D) {
+              // what the ranks before this one sent, decayed from the first token of the sequence to the span
+              if (!link_receive<kHalfE, D>(a.link, step_x, elems, seq_off, row, half * kHalfE,
+                                           decay_pow(sl2, w.t0 * C), P, sn))
+                atomicOr(fault, kFaultRelayWait);
+            }
+          }
         }
         if (row < D) write_state_operand<kHalfE>(sp, D, row, half * kHalfE, P);
         fence_async_smem();
@@ -649,13 +794,19 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
   if (tid == 64) GTRACE(58);
   if (warp == 2) tmem_dealloc(tmem, 512);
   if constexpr (FUSED) {
-    // the last CTA to finish advances the launch counter: the flags of this launch are stale from then on
-    if (tid == 0 && a.nspans > 1) {
+    // the last CTA to finish advances the launch counter: the flags of this launch are stale from then on;
+    // with a link it also tells the ranks before this one that their words have been read (they may
+    // overwrite them two hand-overs later) and completes the hand-over
+    if (tid == 0 && a.coop) {
       __threadfence();
       if (atomicAdd(a.sync + 1, 1u) == gridDim.x - 1) {
         st_volatile_u32(a.sync + 1, 0u);
         __threadfence();
         st_volatile_u32(a.sync, step_s);
+        if (a.link.ranks > 0) {
+          for (int q = 0; q < a.link.me; ++q) st_volatile_u32(a.link.src_acks[q] + xl::ack_index(a.link.me, 0), step_x);
+          st_volatile_u32(a.link.counters, step_x);
+        }
       }
     }
   }
@@ -701,7 +852,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
   __shared__ uint64_t kv_full[2], staged[2];
   __shared__ uint64_t qdo_full, dn_ready, a_done, ms_ready, sm_ready, b_done, l_done, e_free, l_free;
   __shared__ uint64_t ring_full[2], ring_scaled[2], ring_empty[2], sum_done;   // the span-total phase
-  __shared__ uint32_t tmem_slot, step_s;
+  __shared__ uint32_t tmem_slot, step_s, step_x;
   __shared__ int dead;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int32_t* fault = a.fault;
@@ -731,7 +882,10 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
     prefetch_tensormap(&map_do);
     prefetch_tensormap(&map_dk);
     prefetch_tensormap(&map_dv);
-    if constexpr (FUSED) step_s = a.nspans > 1 ? ld_volatile_u32(a.sync) + 1 : 0;
+    if constexpr (FUSED) {
+      step_s = a.coop ? ld_volatile_u32(a.sync) + 1 : 0;                       // this launch among those on the workspace
+      step_x = a.link.ranks > 0 ? ld_volatile_u32(a.link.counters) + 1 : 0;    // this hand-over in the group
+    }
   }
   if (warp == 2) tmem_alloc(&tmem_slot, 512);
   tc_fence_before_sync();
@@ -745,7 +899,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
   bool sums = false;
   int sum_t0 = 0, sum_t1 = 0, my_bh = 0, my_sp = 0;
   if constexpr (FUSED) {
-    if (a.nspans > 1 && w.start(blockIdx.x, gridDim.x)) {
+    if (a.coop && w.start(blockIdx.x, gridDim.x)) {
       my_bh = w.bh;
       my_sp = w.it - w.bh * a.nspans;
       sum_t0 = w.t0;
@@ -930,6 +1084,34 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
               fma_state<kHalfE, D>(a.totals + (size_t)(w.bh * a.nspans + j) * D * E, row, half * kHalfE,
                                    decay_pow(sl2, (j - sp_idx - 1) * a.span * C), Dn);
           }
+          if (a.link.ranks > 0) {
+            // hand-over of the rank state inside the launch.  Dn holds the local part of the border state.
+            const float sn = a.s[w.bh % a.h] * (float)a.n;
+            const long long elems = (long long)(a.items / a.nspans) * D * E;
+            const size_t seq_off = (size_t)w.bh * D * E;
+            const int n_dst = a.link.ranks - 1 - a.link.me;
+            if (sp_idx == 0 && n_dst > 0) {
+              // this CTA owns the start of the sequence: the sequence's total, lambda^(span end) Dn + T, goes
+              // to the ranks after this one in the chain order (the ranks BEFORE it in the sequence)
+              if (xl::needs_ack_wait(step_x) && tid - 64 < n_dst && !dead) {
+                if (!wait_flag_ge(a.link.my_acks + xl::ack_index(a.link.me + 1 + (tid - 64), 0), step_x - 2,
+                                  a.link.wait_clocks)) {
+                  dead = 1;
+                  atomicOr(fault, kFaultRelayWait);
+                }
+              }
+              named_sync(1, kWorkers);
+              if (row < D)
+                link_send<kHalfE, D>(a.link, step_x, elems, seq_off, row, half * kHalfE, decay_pow(sl2, span_end), Dn,
+                                     a.totals + (size_t)w.it * D * E, sn);
+            }
+            if (a.link.me > 0 && row < D) {
+              // what came from the ranks after this one in the sequence, decayed from its end to the span's
+              if (!link_receive<kHalfE, D>(a.link, step_x, elems, seq_off, row, half * kHalfE,
+                                           decay_pow(sl2, a.n - span_end), Dn, sn))
+                atomicOr(fault, kFaultRelayWait);
+            }
+          }
         }
         // the phase-A MMAs that read the operand tile of the previous item have completed (a_done was waited for)
         if (row < D) write_state_operand<kHalfE>(sdn, D, row, half * kHalfE, Dn);
@@ -1042,12 +1224,16 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
   if (tid == 64) GTRACE(58);
   if (warp == 2) tmem_dealloc(tmem, 512);
   if constexpr (FUSED) {
-    if (tid == 0 && a.nspans > 1) {
+    if (tid == 0 && a.coop) {
       __threadfence();
       if (atomicAdd(a.sync + 1, 1u) == gridDim.x - 1) {
         st_volatile_u32(a.sync + 1, 0u);
         __threadfence();
         st_volatile_u32(a.sync, step_s);
+        if (a.link.ranks > 0) {
+          for (int q = 0; q < a.link.me; ++q) st_volatile_u32(a.link.src_acks[q] + xl::ack_index(a.link.me, 0), step_x);
+          st_volatile_u32(a.link.counters, step_x);
+        }
       }
     }
   }
@@ -1132,7 +1318,9 @@ cudaError_t launch_walk_out(const Dims& m, const void* x, const void* y, const v
   if ((err = opt_in_smem(k_walk_out<D, E, DQ, FUSED>, smem)) != cudaSuccess) return err;
   a.h = m.h, a.n = m.n, a.tiles = m.tiles, a.span = m.span, a.nspans = m.nc, a.items = m.b * m.h * m.nc;
   a.wait_clocks = kFlagWaitClocks;
-  const bool waits = FUSED && m.nc > 1;   // CTAs wait for one another: one span each, all resident
+  const bool waits = FUSED && (m.nc > 1 || a.link.ranks > 0);   // CTAs wait for one another: one span each, all resident
+  a.coop = waits ? 1 : 0;
+  if (a.link.ranks > 0 && a.link.me < a.link.ranks - 1) a.all_totals = 1;   // the sequence totals are sent on
   if (waits && a.items > sm_count()) {
     g_failed_step = "fused walk kernel: more spans than SMs";
     return cudaErrorInvalidConfiguration;
@@ -1161,7 +1349,9 @@ cudaError_t launch_walk_dkv(const Dims& m, const void* q, const void* k, const v
   if ((err = opt_in_smem(k_walk_dkv<D, E, FUSED>, smem)) != cudaSuccess) return err;
   a.h = m.h, a.n = m.n, a.tiles = m.tiles, a.span = m.span, a.nspans = m.nc, a.items = m.b * m.h * m.nc;
   a.wait_clocks = kFlagWaitClocks;
-  const bool waits = FUSED && m.nc > 1;
+  const bool waits = FUSED && (m.nc > 1 || a.link.ranks > 0);
+  a.coop = waits ? 1 : 0;
+  if (a.link.ranks > 0 && a.link.me < a.link.ranks - 1) a.all_totals = 1;
   if (waits && a.items > sm_count()) {
     g_failed_step = "fused walk kernel: more spans than SMs";
     return cudaErrorInvalidConfiguration;
@@ -1201,10 +1391,28 @@ cudaError_t walk_fwd_output(const Dims& m, const void* q, const void* k, const v
 #undef LASP_CALL
 }
 
+// the walk kernels' view of the caller's peer-mapped buffers (NULL: no link)
+static Link make_link(const lasp_exchange_args* x) {
+  Link l = {};
+  if (x == nullptr) return l;
+  l.my_slots = static_cast<const uint2*>(x->my_slots);
+  l.my_acks = x->my_acks;
+  l.counters = x->counters;
+  for (int i = 0; i < xl::kMaxRanks; ++i) {
+    l.src_acks[i] = x->peer_acks[i];
+    l.dst_slots[i] = static_cast<uint2*>(x->peer_slots[i]);
+  }
+  l.ranks = x->ranks;
+  l.me = x->position;
+  l.wait_clocks = x->wait_clocks > 0 ? x->wait_clocks : 20000000000LL;   // about ten seconds
+  return l;
+}
+
 cudaError_t walk_fwd_fused(const Dims& m, const void* q, const void* k, const void* v, const float* s,
                            const float* x_in, float* x_out, uint32_t* sync, float* totals, float* prefix, void* o,
-                           cudaStream_t st) {
+                           const lasp_exchange_args* link, cudaStream_t st) {
   WalkArgs a = {};
+  a.link = make_link(link);
   a.s = s, a.x_in = x_in, a.x_out = x_out, a.sync = sync, a.totals = totals, a.p0_save = prefix;
 #define LASP_CALL(DD, EE) launch_walk_out<DD, EE, false, true>(m, q, k, v, o, a, st)
   LASP_DISPATCH_DE(m, LASP_CALL);
@@ -1231,8 +1439,9 @@ cudaError_t walk_bwd_dkv(const Dims& m, const void* q, const void* k, const void
 
 cudaError_t walk_bwd_dkv_fused(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
                                const float* s, const float* x_in, float* x_out, uint32_t* sync, float* totals,
-                               void* dk, void* dv, cudaStream_t st) {
+                               void* dk, void* dv, const lasp_exchange_args* link, cudaStream_t st) {
   WalkArgs a = {};
+  a.link = make_link(link);
   a.s = s, a.x_in = x_in, a.x_out = x_out, a.sync = sync, a.totals = totals;
 #define LASP_CALL(DD, EE) launch_walk_dkv<DD, EE, true>(m, q, k, v, d_o, dk, dv, a, st)
   LASP_DISPATCH_DE(m, LASP_CALL);

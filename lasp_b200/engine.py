@@ -160,6 +160,13 @@ class Forward:
         self._call("lasp_b200_forward")
         return self.o
 
+    def run_linked(self, link_args):
+        """The whole forward of a sequence-parallel rank in one launch (lasp_b200_forward_linked)."""
+        with _on_device(self.q.device), _traced("lasp_b200_forward_linked"):
+            _cabi.call("lasp_b200_forward_linked", C.byref(self.plan.problem), C.byref(self._args),
+                       C.byref(link_args), _stream())
+        return self.o
+
 
 class Backward:
     """One backward call split in its three phases."""
@@ -197,6 +204,12 @@ class Backward:
     def dkv_after_scan(self):
         self._call("lasp_b200_bwd_dkv_walk")
 
+    def dkv_linked(self, link_args):
+        """dK, dV of a sequence-parallel rank with the hand-over inside the launch."""
+        with _on_device(self.keep[0].device), _traced("lasp_b200_bwd_dkv_linked"):
+            _cabi.call("lasp_b200_bwd_dkv_linked", C.byref(self.plan.problem), C.byref(self._args),
+                       C.byref(link_args), _stream())
+
     def run(self):
         self._call("lasp_b200_backward")
         return self.dq, self.dk, self.dv
@@ -211,6 +224,11 @@ def state_combine(s, x_in, x_local, n: int, out=None):
         _cabi.call("lasp_b200_state_combine", b, h, d, e, n, _ptr(_slopes(s, h, x_local.device)), _ptr(x_in),
                    _ptr(x_local), _ptr(out), _stream())
     return out
+
+
+def linked_ok(plan: Plan) -> bool:
+    """True when the fused kernels can do the hand-over themselves for this problem (one span per SM)."""
+    return _cabi.call("lasp_b200_linked_ok", C.byref(plan.problem)) == 1
 
 
 def exchange_scan(plan: Plan, args: "_cabi.ExchangeArgs", device) -> None:

@@ -2,9 +2,10 @@
 
 ``FixedStep`` binds one set of input/output tensors to the C-ABI launches of a
 forward and a backward pass: on a single device three kernels on the tensor-core
-path (fused forward, dQ walk, fused dK/dV walk; six on the fp32 path); as a rank
-of a sequence-parallel group seven (span totals, hand-over + scan, walk, twice,
-the backward walk being two kernels).  Nothing is allocated by ``run()``, and no NCCL call
+path (fused forward, dQ walk, fused dK/dV walk; six on the fp32 path).  As a rank
+of a sequence-parallel group the same three, the two fused ones handing the rank
+state over inside the launch; when the spans do not fit one per SM, eight (span
+totals, hand-over in two halves around dQ, scan, walks).  Nothing is allocated by ``run()``, and no NCCL call
 is made, so the whole step can be captured in a CUDA graph and replayed.
 It issues exactly the launches the autograd functions of ``_core`` issue.
 """
@@ -31,11 +32,14 @@ class FixedStep:
                 raise RuntimeError("FixedStep needs the peer-mapped relay transport (LASP_B200_TRANSPORT=nvlink)")
         self.fw = engine.Forward(self.plan, q, k, v, s)
         self.bw = engine.Backward(self.plan, q, k, v, do, s, self.fw.ws)
+        self.linked = self.relay is not None and engine.linked_ok(self.plan)
+        if self.linked:
+            self.link_f, self.link_b = self.relay.link_args(backward=False), self.relay.link_args(backward=True)
 
     @property
     def launches(self) -> int:
         tensor = self.plan.path_name == "tensor"
-        if self.relay is None:
+        if self.relay is None or self.linked:
             return 3 if tensor else 6
         return 8 if tensor else 7
 
@@ -48,6 +52,15 @@ class FixedStep:
         if self.relay is None:
             fw.run()
             bw.run()
+            return
+        if self.linked:
+            fw.run_linked(self.link_f)
+            if self.rank == self.last:        # nobody to wait for in the backward pass: send first
+                bw.dkv_linked(self.link_b)
+                bw.dq_only()
+            else:
+                bw.dq_only()
+                bw.dkv_linked(self.link_b)
             return
         fw.chunk_states()
         self.relay.exchange_scan(self.plan, fw.ws, self.s, backward=False)
