@@ -545,8 +545,9 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
         bool need_o2 = true, need_l = true, need_o1 = true, need_s = i + 1 < total;
         const long long t0 = clock64();
         while ((need_o2 || need_l || need_o1 || need_s) && !dead) {
-          // O1 = S_m Z on top of the row-scaled O2, the masked scores read from tensor memory
-          if (need_o1 && !need_o2 && mbar_test_wait(&sm_ready[p], ph) && mbar_test_wait(&o2s_ready, one) &&
+          // O1 = S_m Z on top of the row-scaled O2, the masked scores read from tensor memory.  It goes out
+          // after L: the commit behind it then also covers L's reads of Y and Z, which is what frees them
+          if (need_o1 && !need_o2 && !need_l && mbar_test_wait(&sm_ready[p], ph) && mbar_test_wait(&o2s_ready, one) &&
               mbar_test_wait(&z_full[p], ph)) {
             TRACE(32 + i * 5 + 3);
             tc_fence_after_sync();
