@@ -245,26 +245,66 @@ __device__ __forceinline__ void st_volatile_v4(void* p, uint4 v) {
                : "memory");
 }
 
+// Where the two 16-byte halves of the four {value, step} words of float4 chunk g, row `row`, of a
+// sequence sit among its slots (in words): per chunk two planes of ROWS x 16 bytes, so that the 32 rows
+// of a warp write - and read - 512 contiguous bytes with each instruction.
+template <int ROWS>
+__device__ __forceinline__ size_t link_word(int g, int row, int plane) {
+  return (size_t)g * ROWS * 4 + (size_t)plane * ROWS * 2 + (size_t)row * 2;
+}
+
 // This thread's part (row `row`, columns [col0, col0 + N)) of a sequence's outgoing total, dec * P + own,
-// stored as {value, step} words into the slots of every rank after this one that it still reaches.  The
-// words of a sequence are in lane order like the states themselves, so sender and receiver are coalesced.
+// written over `own` (the total of the sequence's last span in walk order, which no other CTA reads).
 template <int N, int ROWS>
-__device__ __forceinline__ void link_send(const Link& l, uint32_t step, long long elems, size_t seq_off, int row,
-                                          int col0, float dec, const float (&P)[N], const float* own, float sn) {
-  const float4* src = reinterpret_cast<const float4*>(own) + (size_t)(col0 / 4) * ROWS + row;
+__device__ __forceinline__ void link_make_total(float* own, int row, int col0, float dec, const float (&P)[N]) {
+  float4* t = reinterpret_cast<float4*>(own) + (size_t)(col0 / 4) * ROWS + row;
+#pragma unroll 4
+  for (int q = 0; q < N / 4; ++q) {
+    const float4 o = __ldcg(t + (size_t)q * ROWS);
+    t[(size_t)q * ROWS] = make_float4(fmaf(dec, P[4 * q], o.x), fmaf(dec, P[4 * q + 1], o.y),
+                                      fmaf(dec, P[4 * q + 2], o.z), fmaf(dec, P[4 * q + 3], o.w));
+  }
+}
+
+// One CTA's share of the sending: of this thread's float4 chunks of the sequence's total, those whose index
+// is `part` modulo `parts`, stored as {value, step} words into the slots of every rank after this one
+// that the state still reaches.  All CTAs of a sequence send, each its share: one SM alone pushes slowly.
+template <int N, int ROWS>
+__device__ __forceinline__ void link_send_part(const Link& l, uint32_t step, long long elems, size_t seq_off, int row,
+                                               int col0, const float* total, float sn, int part, int parts) {
+  const float4* src = reinterpret_cast<const float4*>(total) + (size_t)(col0 / 4) * ROWS + row;
   const int n_dst = l.ranks - 1 - l.me;
+#pragma unroll 4
+  for (int q = 0; q < N / 4; ++q) {
+    if ((col0 / 4 + q) % parts != part) continue;
+    const float4 t = __ldcg(src + (size_t)q * ROWS);
+    for (int di = 0; di < n_dst; ++di) {
+      if (!xl::reaches(sn, di)) break;   // farther ranks are out of reach too
+      uint2* out = l.dst_slots[l.me + 1 + di] + xl::slot_offset(step & 1, l.ranks, l.me, elems) + seq_off;
+      st_volatile_v4(out + link_word<ROWS>(col0 / 4 + q, row, 0),
+                     make_uint4(__float_as_uint(t.x), step, __float_as_uint(t.y), step));
+      st_volatile_v4(out + link_word<ROWS>(col0 / 4 + q, row, 1),
+                     make_uint4(__float_as_uint(t.z), step, __float_as_uint(t.w), step));
+    }
+  }
+}
+
+// The whole of this thread's part of the total, dec * P + own, straight from registers to the NEXT rank
+// only (for sequences whose state reaches no farther: nothing to share out, no detour through memory).
+template <int N, int ROWS>
+__device__ __forceinline__ void link_send_next(const Link& l, uint32_t step, long long elems, size_t seq_off, int row,
+                                               int col0, float dec, const float (&P)[N], const float* own) {
+  const float4* src = reinterpret_cast<const float4*>(own) + (size_t)(col0 / 4) * ROWS + row;
+  uint2* out = l.dst_slots[l.me + 1] + xl::slot_offset(step & 1, l.ranks, l.me, elems) + seq_off;
 #pragma unroll 4
   for (int q = 0; q < N / 4; ++q) {
     const float4 o = __ldcg(src + (size_t)q * ROWS);
     const float4 t = make_float4(fmaf(dec, P[4 * q], o.x), fmaf(dec, P[4 * q + 1], o.y), fmaf(dec, P[4 * q + 2], o.z),
                                  fmaf(dec, P[4 * q + 3], o.w));
-    const size_t word = seq_off + ((size_t)(col0 / 4 + q) * ROWS + row) * 4;
-    for (int di = 0; di < n_dst; ++di) {
-      if (!xl::reaches(sn, di)) break;   // farther ranks are out of reach too
-      uint2* out = l.dst_slots[l.me + 1 + di] + xl::slot_offset(step & 1, l.ranks, l.me, elems) + word;
-      st_volatile_v4(out, make_uint4(__float_as_uint(t.x), step, __float_as_uint(t.y), step));
-      st_volatile_v4(out + 2, make_uint4(__float_as_uint(t.z), step, __float_as_uint(t.w), step));
-    }
+    st_volatile_v4(out + link_word<ROWS>(col0 / 4 + q, row, 0),
+                   make_uint4(__float_as_uint(t.x), step, __float_as_uint(t.y), step));
+    st_volatile_v4(out + link_word<ROWS>(col0 / 4 + q, row, 1),
+                   make_uint4(__float_as_uint(t.z), step, __float_as_uint(t.w), step));
   }
 }
 
@@ -279,24 +319,32 @@ __device__ __forceinline__ bool link_receive(const Link& l, uint32_t step, long 
     if (!xl::reaches(sn, hops)) break;   // farther ranks are out of reach too
     const float wgt = dec * expf(-sn * (float)hops);
     const uint2* in = l.my_slots + xl::slot_offset(step & 1, l.ranks, src, elems) + seq_off;
+    // wait with pauses on this thread's last word before touching the rest: thousands of threads
+    // re-reading all their words would only get in the way of the stores that are arriving
+    {
+      const uint2* p = in + link_word<ROWS>(col0 / 4 + N / 4 - 1, row, 1);
+      const long long t0 = clock64();
+      while (!late && ld_volatile_v4(p).w != step) {
+        __nanosleep(100);
+        if (clock64() - t0 > l.wait_clocks) late = true;
+      }
+    }
     constexpr int kBatch = 4;   // float4 chunks in flight
 #pragma unroll
     for (int q0 = 0; q0 < N / 4; q0 += kBatch) {
       uint4 w0[kBatch], w1[kBatch];
 #pragma unroll
       for (int u = 0; u < kBatch; ++u) {
-        const uint2* p = in + ((size_t)(col0 / 4 + q0 + u) * ROWS + row) * 4;
-        w0[u] = ld_volatile_v4(p);
-        w1[u] = ld_volatile_v4(p + 2);
+        w0[u] = ld_volatile_v4(in + link_word<ROWS>(col0 / 4 + q0 + u, row, 0));
+        w1[u] = ld_volatile_v4(in + link_word<ROWS>(col0 / 4 + q0 + u, row, 1));
       }
 #pragma unroll
       for (int u = 0; u < kBatch; ++u) {
         if (!late && (w0[u].y != step || w0[u].w != step || w1[u].y != step || w1[u].w != step)) {
-          const uint2* p = in + ((size_t)(col0 / 4 + q0 + u) * ROWS + row) * 4;
           const long long t0 = clock64();   // after one wait has run out this thread waits no more
           do {
-            w0[u] = ld_volatile_v4(p);
-            w1[u] = ld_volatile_v4(p + 2);
+            w0[u] = ld_volatile_v4(in + link_word<ROWS>(col0 / 4 + q0 + u, row, 0));
+            w1[u] = ld_volatile_v4(in + link_word<ROWS>(col0 / 4 + q0 + u, row, 1));
             if (clock64() - t0 > l.wait_clocks) {
               late = true;
               break;
@@ -333,7 +381,8 @@ struct WalkArgs {
   const float* p0;     // not fused: fp32 state of every span at its border, [items][D][E] (from the scan)
   float* p0_save;      // fused: where the border states are kept for the backward pass (may be NULL)
   float* totals;       // fused: span totals [items][D][E], exchanged between the CTAs of the launch
-  uint32_t* sync;      // fused: [0] launch counter, [1] CTAs done, [kSyncFlags + item] "total written" flags
+  uint32_t* sync;      // fused: [0] launch counter, [1] CTAs done, [kSyncFlags + item] "total written" flags,
+                       // [kSyncFlags + kSyncSecondBank + sequence] "sequence total written" flags (4 KB in all)
   const float* x_in;   // fused: incoming rank state (b,h,d,e) or NULL
   float* x_out;        // fused: outgoing rank state (b,h,d,e) or NULL
   int h, n, tiles, span, nspans, items;
@@ -345,6 +394,7 @@ struct WalkArgs {
   Link link;           // fused: hand the rank state over inside the launch (link.ranks > 0)
 };
 constexpr int kSyncFlags = 32;
+constexpr int kSyncSecondBank = 480;   // [kSyncFlags + kSyncSecondBank + sequence]: "the sequence's total is written"
 
 // bf16 image of this thread's part of the state (row `row`, columns [col0, col0 + N)) in the operand tile
 template <int N>
@@ -698,33 +748,60 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
               fma_state<kHalfE, D>(a.totals + (size_t)(w.bh * a.nspans + j) * D * E, row, half * kHalfE,
                                    decay_pow(sl2, (sp_idx - 1 - j) * a.span * C), P);
           }
+          if (tid == 64) TRACE(61);
           if (a.link.ranks > 0) {
             // hand-over of the rank state inside the launch.  P holds the local part of the border state.
             const float sn = a.s[w.bh % a.h] * (float)a.n;
             const long long elems = (long long)(a.items / a.nspans) * D * E;
             const size_t seq_off = (size_t)w.bh * D * E;
             const int n_dst = a.link.ranks - 1 - a.link.me;
-            if (sp_idx == a.nspans - 1 && n_dst > 0) {
-              // this CTA owns the end of the sequence: the sequence's total, lambda^(n - start) P + T, goes to
-              // the ranks after this one (whose readers acknowledged the slot's previous use)
-              if (xl::needs_ack_wait(step_x) && tid - 64 < n_dst && !dead) {
-                if (!wait_flag_ge(a.link.my_acks + xl::ack_index(a.link.me + 1 + (tid - 64), 0), step_x - 2,
-                                  a.link.wait_clocks)) {
-                  dead = 1;
-                  atomicOr(fault, kFaultRelayWait);
+            if (n_dst > 0) {
+              const int owner = w.bh * a.nspans + a.nspans - 1;   // the CTA that owns the end of the sequence
+              const bool far = n_dst > 1 && xl::reaches(sn, 1);   // the state reaches beyond the next rank
+              uint32_t* ready = a.sync + kSyncFlags + kSyncSecondBank + w.bh;
+              if (w.it == owner && far) {
+                // the sequence's total, lambda^(n - start) P + T, where the other CTAs of the sequence find it
+                if (row < D)
+                  link_make_total<kHalfE, D>(a.totals + (size_t)owner * D * E, row, half * kHalfE,
+                                             decay_pow(sl2, a.n - w.t0 * C), P);
+                named_sync(1, kWorkers);
+                if (tid == 64) {
+                  __threadfence();
+                  st_volatile_u32(ready, step_s);
                 }
               }
-              named_sync(1, kWorkers);
-              if (row < D)
-                link_send<kHalfE, D>(a.link, step_x, elems, seq_off, row, half * kHalfE,
-                                     decay_pow(sl2, a.n - w.t0 * C), P, a.totals + (size_t)w.it * D * E, sn);
+              if (far || w.it == owner) {
+                // the readers of the ranks after this one have acknowledged the slots' previous use
+                if (!dead) {
+                  bool ok = true;
+                  if (xl::needs_ack_wait(step_x) && tid - 64 < n_dst)
+                    ok = wait_flag_ge(a.link.my_acks + xl::ack_index(a.link.me + 1 + (tid - 64), 0), step_x - 2,
+                                      a.link.wait_clocks);
+                  if (far && tid == 64 + xl::kMaxRanks && w.it != owner) ok = wait_flag_eq(ready, step_s, a.wait_clocks);
+                  if (!ok) {
+                    dead = 1;
+                    atomicOr(fault, kFaultRelayWait);
+                  }
+                }
+                named_sync(1, kWorkers);
+                if (row < D) {
+                  if (far)   // several destinations: every CTA of the sequence sends its share
+                    link_send_part<kHalfE, D>(a.link, step_x, elems, seq_off, row, half * kHalfE,
+                                              a.totals + (size_t)owner * D * E, sn, sp_idx, a.nspans);
+                  else       // the next rank only: straight from the owner's registers
+                    link_send_next<kHalfE, D>(a.link, step_x, elems, seq_off, row, half * kHalfE,
+                                              decay_pow(sl2, a.n - w.t0 * C), P, a.totals + (size_t)owner * D * E);
+                }
+              }
             }
+            if (tid == 64) TRACE(62);
             if (a.link.me > 0 && row < D) {
               // what the ranks before this one sent, decayed from the first token of the sequence to the span
               if (!link_receive<kHalfE, D>(a.link, step_x, elems, seq_off, row, half * kHalfE,
                                            decay_pow(sl2, w.t0 * C), P, sn))
                 atomicOr(fault, kFaultRelayWait);
             }
+            if (tid == 64) TRACE(55);
           }
         }
         if (row < D) write_state_operand<kHalfE>(sp, D, row, half * kHalfE, P);
@@ -1091,20 +1168,45 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
             const long long elems = (long long)(a.items / a.nspans) * D * E;
             const size_t seq_off = (size_t)w.bh * D * E;
             const int n_dst = a.link.ranks - 1 - a.link.me;
-            if (sp_idx == 0 && n_dst > 0) {
-              // this CTA owns the start of the sequence: the sequence's total, lambda^(span end) Dn + T, goes
-              // to the ranks after this one in the chain order (the ranks BEFORE it in the sequence)
-              if (xl::needs_ack_wait(step_x) && tid - 64 < n_dst && !dead) {
-                if (!wait_flag_ge(a.link.my_acks + xl::ack_index(a.link.me + 1 + (tid - 64), 0), step_x - 2,
-                                  a.link.wait_clocks)) {
-                  dead = 1;
-                  atomicOr(fault, kFaultRelayWait);
+            if (n_dst > 0) {
+              const int owner = w.bh * a.nspans;   // the CTA that owns the start of the sequence
+              const bool far = n_dst > 1 && xl::reaches(sn, 1);   // the state reaches beyond the next rank
+              uint32_t* ready = a.sync + kSyncFlags + kSyncSecondBank + w.bh;
+              if (w.it == owner && far) {
+                // the sequence's total, lambda^(span end) Dn + T, where the other CTAs of the sequence find it
+                if (row < D)
+                  link_make_total<kHalfE, D>(a.totals + (size_t)owner * D * E, row, half * kHalfE,
+                                             decay_pow(sl2, span_end), Dn);
+                named_sync(1, kWorkers);
+                if (tid == 64) {
+                  __threadfence();
+                  st_volatile_u32(ready, step_s);
                 }
               }
-              named_sync(1, kWorkers);
-              if (row < D)
-                link_send<kHalfE, D>(a.link, step_x, elems, seq_off, row, half * kHalfE, decay_pow(sl2, span_end), Dn,
-                                     a.totals + (size_t)w.it * D * E, sn);
+              if (far || w.it == owner) {
+                // the readers of the ranks after this one in the chain order (the ranks BEFORE it in the
+                // sequence) have acknowledged the slots' previous use
+                if (!dead) {
+                  bool ok = true;
+                  if (xl::needs_ack_wait(step_x) && tid - 64 < n_dst)
+                    ok = wait_flag_ge(a.link.my_acks + xl::ack_index(a.link.me + 1 + (tid - 64), 0), step_x - 2,
+                                      a.link.wait_clocks);
+                  if (far && tid == 64 + xl::kMaxRanks && w.it != owner) ok = wait_flag_eq(ready, step_s, a.wait_clocks);
+                  if (!ok) {
+                    dead = 1;
+                    atomicOr(fault, kFaultRelayWait);
+                  }
+                }
+                named_sync(1, kWorkers);
+                if (row < D) {
+                  if (far)
+                    link_send_part<kHalfE, D>(a.link, step_x, elems, seq_off, row, half * kHalfE,
+                                              a.totals + (size_t)owner * D * E, sn, sp_idx, a.nspans);
+                  else
+                    link_send_next<kHalfE, D>(a.link, step_x, elems, seq_off, row, half * kHalfE,
+                                              decay_pow(sl2, span_end), Dn, a.totals + (size_t)owner * D * E);
+                }
+              }
             }
             if (a.link.me > 0 && row < D) {
               // what came from the ranks after this one in the sequence, decayed from its end to the span's
