@@ -210,6 +210,52 @@ def run_reference(args, cfg):
     print(json.dumps(line), flush=True)
 
 
+def run_reference_triton(args, cfg):
+    """Informational, never the reference arm: the reference's own Triton kernels (lightning_attn, single
+    device) from the unmodified install under baseline/_ref, JIT-compiled for this GPU by the installed Triton,
+    on the same shape, dtype, steps and warm-up.  Prints `unavailable` with the reason when that cannot run."""
+    if env_int("RANK", 0) != 0:
+        return
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    line = {"impl": "reference-triton", "metric": metric_name(cfg), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": cfg["text"] + " - lightning_attn of the reference on one GPU"}}
+    try:
+        if not os.path.isdir(os.path.join(ref_dir, "lasp")):
+            raise RuntimeError("baseline/_ref holds no install of the reference")
+        sys.path[:] = [ref_dir] + [p for p in sys.path if os.path.abspath(p or ".") != ROOT]
+        for name in [m for m in sys.modules if m == "lasp" or m.startswith("lasp.")]:
+            del sys.modules[name]
+        import lasp as ref_lasp
+        if not os.path.abspath(ref_lasp.__file__).startswith(ref_dir):
+            raise RuntimeError(f"imported {ref_lasp.__file__}, not the install under baseline/_ref")
+        device = torch.device("cuda", 0)
+        torch.cuda.set_device(device)
+        q, k, v, do = make_set(cfg, 1000, device, torch.bfloat16)
+        s = slopes_for(cfg).to(device)
+        for t in (q, k, v):
+            t.requires_grad_(True)
+
+        def step():
+            q.grad = k.grad = v.grad = None
+            ref_lasp.lightning_attn(q, k, v, s).backward(do)
+
+        for _ in range(args.warmup):
+            step()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(args.steps):
+            step()
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / args.steps
+        line.update(value=cfg["b"] * cfg["n"] / (ms * 1e-3), ms_per_step=ms, higher_is_better=True)
+    except BaseException as exc:  # noqa: BLE001  (a Triton compile error must become the line, not a crash)
+        line["unavailable"] = f"{type(exc).__name__}: {str(exc).splitlines()[0] if str(exc) else ''}"[:300]
+    print(json.dumps(line), flush=True)
+
+
 def metric_name(cfg):
     return (f"fwd+bwd tokens/s, LASP linear attention (b={cfg['b']}/rank, h={cfg['h']}, {cfg['n']} tokens/rank, "
             f"d={cfg['d']}, e={cfg['e']})")
@@ -218,6 +264,24 @@ def metric_name(cfg):
 # ---------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------
+def run_kernels_only(args, cfg):
+    """What a profiler run wants: the launches of W + K steps on rotating input sets, nothing around them."""
+    from lasp_b200 import engine
+    from lasp_b200.pipeline import FixedStep
+    b, h, n, d, e = (cfg[x] for x in "bhnde")
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    s = slopes_for(cfg).to(device)
+    set_bytes = (2 * d + 2 * e) * 2 * b * h * n
+    n_sets = max(2, min(6, int(L2_BYTES * 1.6 // set_bytes) + 1))
+    steps = [FixedStep(*make_set(cfg, 1000 + i, device, torch.bfloat16), s) for i in range(n_sets)]
+    for i in range(args.warmup + args.steps):
+        steps[i % n_sets].run()
+    torch.cuda.synchronize()
+    print(json.dumps({"kernels_only": True, "steps": args.steps, "warmup": args.warmup, "launches_per_step":
+                      steps[0].launches, "config": args.config, "kernel_faults": engine.read_status()}), flush=True)
+
+
 def run_ours(args, cfg):
     import torch.distributed as dist
     import lasp_b200
@@ -550,15 +614,21 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-triton"])
     ap.add_argument("--config", default="cfg1", choices=sorted(CONFIGS))
     ap.add_argument("--dp", type=int, default=1, help="data-parallel size; sequence-parallel size = gpus / dp")
     ap.add_argument("--eager", action="store_true", help="time the public operator launch by launch (no CUDA graph)")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="W + K steps of the C-ABI launches on one GPU and nothing else (the target of profiler runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     cfg = CONFIGS[args.config]
     if args.impl == "reference":
         run_reference(args, cfg)
+    elif args.impl == "reference-triton":
+        run_reference_triton(args, cfg)
+    elif args.kernels_only:
+        run_kernels_only(args, cfg)
     else:
         run_ours(args, cfg)
 

@@ -34,8 +34,29 @@ def sliced_apply(fn, q, k, v, state_bufs=()):
     the op is a sum over 128-wide q,k slices.  Wider v than 128 is handled the
     same way in the other direction (outputs of v slices are concatenated).
     ``state_bufs`` are (b,h,d,e) buffers sliced alongside.
+
+    When both widths are multiples of 128 the (q/k slice, v slice) pairs are stacked
+    along the batch dimension and go through ONE call - for a sequence-parallel
+    operator one state hand-over per direction instead of one per slice (the
+    reference runs a separate chain per slice, lasp/lasp_fuse.py:546-559).
     """
     d, e = q.shape[-1], v.shape[-1]
+    nd, ne = d // MAX_HEAD_SLICE, e // MAX_HEAD_SLICE
+    if d % MAX_HEAD_SLICE == 0 and e % MAX_HEAD_SLICE == 0 and nd * ne > 1:
+        b, h, n = q.shape[:3]
+        w = MAX_HEAD_SLICE
+
+        def stack(t, parts, over_e):
+            # (b,h,n,parts*w) -> (ne*nd*b, h, n, w), batch index = (v slice, q/k slice, batch row)
+            t = t.reshape(b, h, n, parts, w).permute(3, 0, 1, 2, 4)                 # (parts,b,h,n,w)
+            t = t[:, None] if over_e else t[None]                                   # (ne|1, nd|1, ...)
+            return t.expand(ne, nd, b, h, n, w).reshape(ne * nd * b, h, n, w).contiguous()
+
+        bufs = [x.reshape(b, h, nd, w, ne, w).permute(4, 2, 0, 1, 3, 5).reshape(ne * nd * b, h, w, w).contiguous()
+                for x in state_bufs]                                                # cut alongside
+        o = fn(stack(q, nd, False), stack(k, nd, False), stack(v, ne, True), *bufs)
+        o = o.reshape(ne, nd, b, h, n, w).sum(dim=1)                                # sum over q/k slices
+        return o.permute(1, 2, 3, 0, 4).reshape(b, h, n, e)                        # v slices side by side
     outs = []
     for e0, e1 in _cuts(e):
         vs = v if (e0, e1) == (0, e) else v[..., e0:e1]
