@@ -208,7 +208,8 @@ int fwd_scan(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs) {
 
 int fwd_output(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs) {
   if (m.walk)
-    return cuda_fail(lasp::walk_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_walk_border(a->ws, m), a->o, cs));
+    return cuda_fail(lasp::walk_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_walk_border(a->ws, m),
+                                           lasp::ws_walk_sync(a->ws), a->o, cs));
   return cuda_fail(lasp::simt_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_prefix(a->ws, m), a->o, cs));
 }
 
@@ -225,7 +226,8 @@ int bwd_scan(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs) {
 int bwd_grads(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs) {
   if (m.walk) {
     // dQ walks forward over the border states the forward pass left in its workspace; dK, dV walk backward
-    int st = cuda_fail(lasp::walk_bwd_dq(m, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m), a->dq, cs));
+    int st = cuda_fail(lasp::walk_bwd_dq(m, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m),
+                                          lasp::ws_walk_sync(a->fwd_ws), a->dq, cs));
     if (st != LASP_OK) return st;
     return cuda_fail(lasp::walk_bwd_dkv(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->ws, m), a->dk,
                                         a->dv, cs));
@@ -296,7 +298,8 @@ int lasp_b200_bwd_dq(const lasp_problem* p, const lasp_bwd_args* a, void* stream
   lasp::Dims m;
   int st = check_bwd(p, a, &m, true);
   if (st != LASP_OK || !m.walk) return st;
-  return cuda_fail(lasp::walk_bwd_dq(m, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m), a->dq,
+  return cuda_fail(lasp::walk_bwd_dq(m, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m),
+                                          lasp::ws_walk_sync(a->fwd_ws), a->dq,
                                      static_cast<cudaStream_t>(stream)));
 }
 
@@ -327,7 +330,8 @@ int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stre
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (fusable(m)) {
     // dQ walks forward over the border states the forward pass kept; dK, dV walk backward in one fused launch
-    if ((st = cuda_fail(lasp::walk_bwd_dq(m, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m), a->dq,
+    if ((st = cuda_fail(lasp::walk_bwd_dq(m, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m),
+                                          lasp::ws_walk_sync(a->fwd_ws), a->dq,
                                           cs))) != LASP_OK)
       return st;
     return cuda_fail(lasp::walk_bwd_dkv_fused(m, a->q, a->k, a->v, a->d_o, a->s, a->dkv_in, a->dkv_out,

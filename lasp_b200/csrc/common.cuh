@@ -52,6 +52,7 @@ __host__ __device__ inline int lane_order_to_row_major(int f4, int rows, int col
 }
 constexpr size_t kWalkSyncBytes = 4096;
 inline uint32_t* ws_walk_sync(void* ws) { return reinterpret_cast<uint32_t*>(ws); }
+inline const uint32_t* ws_walk_sync(const void* ws) { return reinterpret_cast<const uint32_t*>(ws); }
 inline float* ws_walk_totals(void* ws) { return reinterpret_cast<float*>(static_cast<char*>(ws) + kWalkSyncBytes); }
 inline float* ws_walk_border(void* ws, const Dims& m) {
   return reinterpret_cast<float*>(static_cast<char*>(ws) + kWalkSyncBytes + state_elems(m) * 4);
@@ -108,12 +109,12 @@ bool tensor_path_supported(const Dims& m);
 cudaError_t walk_span_totals(const Dims& m, const void* a, const void* bten, const float* s, float* totals,
                              bool reverse, cudaStream_t st);
 cudaError_t walk_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
-                            const float* prefix, void* o, cudaStream_t st);
+                            const float* prefix, uint32_t* sync, void* o, cudaStream_t st);
 cudaError_t walk_fwd_fused(const Dims& m, const void* q, const void* k, const void* v, const float* s,
                            const float* x_in, float* x_out, uint32_t* sync, float* totals, float* prefix, void* o,
                            const lasp_exchange_args* link, cudaStream_t st);
 cudaError_t walk_bwd_dq(const Dims& m, const void* k, const void* v, const void* d_o, const float* s,
-                        const float* prefix, void* dq, cudaStream_t st);
+                        const float* prefix, const uint32_t* fwd_sync, void* dq, cudaStream_t st);
 cudaError_t walk_bwd_dkv(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
                          const float* s, const float* suffix, void* dk, void* dv, cudaStream_t st);
 cudaError_t walk_bwd_dkv_fused(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,

@@ -189,17 +189,28 @@ __device__ __forceinline__ void scale_row_pieces(uint8_t* tile, int row, int fir
 
 // The work of a persistent CTA: items blockIdx.x, blockIdx.x + gridDim.x, ...; an item is one span of
 // consecutive tiles of one (batch, head) sequence, walked first to last tile or last to first.
+// Spans: `span` tiles each, the last one of a sequence whatever is left (even = false), or - for a
+// kernel whose CTAs wait for one another - the tiles shared out evenly, spans differing by one tile at
+// most, with the longer spans where the walk starts: there nobody has to wait for anybody's total, and the
+// spans with the longest look-back get the fewest tiles (even = true).
 struct TileWalk {
   int items, nspans, span, tiles, stride;
   bool backwards;
+  bool even;
   int it, bh, t, t0, t1;  // current item, its sequence, current tile, the item's tile range [t0, t1)
 
+  // first tile of span sp (sp = nspans: one past the last tile)
+  __device__ __forceinline__ int span_t0(int sp) const {
+    if (!even) return min(sp * span, tiles);
+    const int base = tiles / nspans, extra = tiles - base * nspans;   // `extra` spans have base + 1 tiles
+    return backwards ? sp * base + max(0, sp - (nspans - extra)) : sp * base + min(sp, extra);
+  }
   __device__ __forceinline__ bool load() {
     if (it >= items) return false;
     bh = it / nspans;
     const int sp = it - bh * nspans;
-    t0 = sp * span;
-    t1 = min(tiles, t0 + span);
+    t0 = span_t0(sp);
+    t1 = span_t0(sp + 1);
     t = backwards ? t1 - 1 : t0;
     return true;
   }

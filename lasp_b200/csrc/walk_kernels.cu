@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(320, 1) k_span_totals(const __grid_constant__ 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
-  TileWalk w{items, nspans, span, tiles, 0, false};
+  TileWalk w{items, nspans, span, tiles, 0, false, false};
 
   if (warp == 0) {
     if (lane == 0) {
@@ -386,6 +386,9 @@ struct WalkArgs {
   const float* x_in;   // fused: incoming rank state (b,h,d,e) or NULL
   float* x_out;        // fused: outgoing rank state (b,h,d,e) or NULL
   int h, n, tiles, span, nspans, items;
+  int even;            // the tiles of a sequence are shared out evenly among its spans (see TileWalk); a fused
+                       // forward records it in sync[kSyncEven], the dQ walk reads it from the forward's workspace
+  const uint32_t* even_word;   // dQ: where the forward pass recorded how it cut the sequences (NULL: a.even)
   int all_totals;      // fused: the last span of a sequence computes its total too
   int coop;            // fused: every CTA has exactly one span and the CTAs synchronise (several spans per
                        // sequence, or a link)
@@ -393,6 +396,7 @@ struct WalkArgs {
   int32_t* fault;
   Link link;           // fused: hand the rank state over inside the launch (link.ranks > 0)
 };
+constexpr int kSyncEven = 2;
 constexpr int kSyncFlags = 32;
 constexpr int kSyncSecondBank = 480;   // [kSyncFlags + kSyncSecondBank + sequence]: "the sequence's total is written"
 
@@ -452,12 +456,13 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
   __shared__ uint64_t x_full[2], y_full[2], z_full[2], s_full[2], sm_ready[2], o_full[2], o2_full[2], staged[2];
   __shared__ uint64_t p_ready, l_free, o_free, ys_ready, o2s_ready, l_full;
   __shared__ uint64_t ring_full[2], ring_scaled[2], ring_empty[2], sum_done;   // the span-total phase
-  __shared__ uint32_t tmem_slot, step_s, step_x;
+  __shared__ uint32_t tmem_slot, step_s, step_x, even_s;
   __shared__ int dead;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int32_t* fault = a.fault;
   if (tid == 0) {
     dead = 0;
+    even_s = a.even_word != nullptr ? ld_volatile_u32(a.even_word) : (uint32_t)a.even;
     for (int p = 0; p < 2; ++p) {
       mbar_init(&x_full[p], 1);
       mbar_init(&y_full[p], 1);
@@ -496,7 +501,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
   if (tid == 64) TRACE(0);
   if (tid == 64) GTRACE(57);
   const uint32_t t_s[2] = {tmem, tmem + 128}, t_o = tmem + 256, t_l = tmem + 384;
-  TileWalk w{a.items, a.nspans, a.span, a.tiles, 0, false};
+  TileWalk w{a.items, a.nspans, a.span, a.tiles, 0, false, even_s != 0};
   // the span-total phase: only with several spans per sequence, and then this CTA has one span
   bool sums = false;
   int sum_t0 = 0, sum_t1 = 0, my_bh = 0, my_sp = 0;
@@ -743,10 +748,10 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
             }
           }
           named_sync(1, kWorkers);
-          for (int j = 0; j < sp_idx; ++j) {
+          for (int j = 0; j < sp_idx; ++j) {   // each total is decayed to the end of its span
             if (row < D)
               fma_state<kHalfE, D>(a.totals + (size_t)(w.bh * a.nspans + j) * D * E, row, half * kHalfE,
-                                   decay_pow(sl2, (sp_idx - 1 - j) * a.span * C), P);
+                                   decay_pow(sl2, (w.t0 - w.span_t0(j + 1)) * C), P);
           }
           if (tid == 64) TRACE(61);
           if (a.link.ranks > 0) {
@@ -871,6 +876,9 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
   if (tid == 64) TRACE(63);
   if (tid == 64) GTRACE(58);
   if (warp == 2) tmem_dealloc(tmem, 512);
+  if constexpr (!DQ) {   // how this pass cut the sequences, for the dQ walk over the border states it leaves
+    if (tid == 0 && blockIdx.x == 0 && a.sync != nullptr) st_volatile_u32(a.sync + kSyncEven, even_s);
+  }
   if constexpr (FUSED) {
     // the last CTA to finish advances the launch counter: the flags of this launch are stale from then on;
     // with a link it also tells the ranks before this one that their words have been read (they may
@@ -973,7 +981,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
   if (tid == 64) TRACE(0);
   if (tid == 64) GTRACE(57);
   const uint32_t t_s = tmem, t_ds = tmem + 128, t_dk = tmem + 256, t_dv = tmem + 384;
-  TileWalk w{a.items, a.nspans, a.span, a.tiles, 0, true};
+  TileWalk w{a.items, a.nspans, a.span, a.tiles, 0, true, a.even != 0};
   bool sums = false;
   int sum_t0 = 0, sum_t1 = 0, my_bh = 0, my_sp = 0;
   if constexpr (FUSED) {
@@ -1157,10 +1165,10 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
             }
           }
           named_sync(1, kWorkers);
-          for (int j = sp_idx + 1; j < a.nspans; ++j) {
+          for (int j = sp_idx + 1; j < a.nspans; ++j) {   // each total is decayed to the start of its span
             if (row < D)
               fma_state<kHalfE, D>(a.totals + (size_t)(w.bh * a.nspans + j) * D * E, row, half * kHalfE,
-                                   decay_pow(sl2, (j - sp_idx - 1) * a.span * C), Dn);
+                                   decay_pow(sl2, (w.span_t0(j) - w.t1) * C), Dn);
           }
           if (a.link.ranks > 0) {
             // hand-over of the rank state inside the launch.  Dn holds the local part of the border state.
@@ -1423,6 +1431,7 @@ cudaError_t launch_walk_out(const Dims& m, const void* x, const void* y, const v
   a.wait_clocks = kFlagWaitClocks;
   const bool waits = FUSED && (m.nc > 1 || a.link.ranks > 0);   // CTAs wait for one another: one span each, all resident
   a.coop = waits ? 1 : 0;
+  if (waits) a.even = 1;
   if (a.link.ranks > 0 && a.link.me < a.link.ranks - 1) a.all_totals = 1;   // the sequence totals are sent on
   if (waits && a.items > sm_count()) {
     g_failed_step = "fused walk kernel: more spans than SMs";
@@ -1454,6 +1463,7 @@ cudaError_t launch_walk_dkv(const Dims& m, const void* q, const void* k, const v
   a.wait_clocks = kFlagWaitClocks;
   const bool waits = FUSED && (m.nc > 1 || a.link.ranks > 0);
   a.coop = waits ? 1 : 0;
+  if (waits) a.even = 1;
   if (a.link.ranks > 0 && a.link.me < a.link.ranks - 1) a.all_totals = 1;
   if (waits && a.items > sm_count()) {
     g_failed_step = "fused walk kernel: more spans than SMs";
@@ -1486,9 +1496,9 @@ cudaError_t walk_span_totals(const Dims& m, const void* a, const void* bten, con
 }
 
 cudaError_t walk_fwd_output(const Dims& m, const void* q, const void* k, const void* v, const float* s,
-                            const float* prefix, void* o, cudaStream_t st) {
+                            const float* prefix, uint32_t* sync, void* o, cudaStream_t st) {
   WalkArgs a = {};
-  a.s = s, a.p0 = prefix;
+  a.s = s, a.p0 = prefix, a.sync = sync;   // sync: only the word that says how the sequences were cut
 #define LASP_CALL(DD, EE) launch_walk_out<DD, EE, false, false>(m, q, k, v, o, a, st)
   LASP_DISPATCH_DE(m, LASP_CALL);
 #undef LASP_CALL
@@ -1523,9 +1533,9 @@ cudaError_t walk_fwd_fused(const Dims& m, const void* q, const void* k, const vo
 }
 
 cudaError_t walk_bwd_dq(const Dims& m, const void* k, const void* v, const void* d_o, const float* s,
-                        const float* prefix, void* dq, cudaStream_t st) {
+                        const float* prefix, const uint32_t* fwd_sync, void* dq, cudaStream_t st) {
   WalkArgs a = {};
-  a.s = s, a.p0 = prefix;
+  a.s = s, a.p0 = prefix, a.even_word = fwd_sync + kSyncEven;   // cut the sequences as the forward pass did
 #define LASP_CALL(DD, EE) launch_walk_out<DD, EE, true, false>(m, d_o, v, k, dq, a, st)
   LASP_DISPATCH_DE(m, LASP_CALL);
 #undef LASP_CALL
