@@ -145,12 +145,20 @@ def feature(t, cfg):
     return torch.nn.functional.elu(t) + 1.0 if cfg["feature_map"] == "elu1" else t
 
 
-def make_set(cfg, seed, device, dtype, pinned=False):
+def qk_preprocessing(cfg):
+    """(scale, feature map) that the configuration puts in front of the operator"""
+    return (cfg["d"] ** -0.5 if cfg["scale_qk"] else 1.0), cfg["feature_map"]
+
+
+def make_set(cfg, seed, device, dtype, pinned=False, raw=False):
+    """raw: q and k as drawn, for the legs that time the preprocessing too (--qk folded | torch)"""
     b, h, n, d, e = (cfg[x] for x in "bhnde")
     g = torch.Generator().manual_seed(seed)
     scale = d ** -0.5 if cfg["scale_qk"] else 1.0
-    q = feature(torch.randn(b, h, n, d, generator=g), cfg) * scale
-    k = feature(torch.randn(b, h, n, d, generator=g), cfg) * scale
+    q = torch.randn(b, h, n, d, generator=g)
+    k = torch.randn(b, h, n, d, generator=g)
+    if not raw:
+        q, k = feature(q, cfg) * scale, feature(k, cfg) * scale
     v = torch.randn(b, h, n, e, generator=g)
     do = torch.randn(b, h, n, e, generator=g)
     ts = [t.to(dtype) for t in (q, k, v, do)]
@@ -264,6 +272,28 @@ def metric_name(cfg):
 # ---------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------
+def bind_to_gpu_numa_node(index):
+    """Restricts this process to the CPUs next to GPU `index` (sysfs local_cpulist of its PCI function), so that
+    the pinned host buffers allocated afterwards are first touched on that node and the copies do not cross the
+    socket interconnect.  Returns the NUMA node, or None when the topology cannot be read."""
+    try:
+        pr = torch.cuda.get_device_properties(index)
+        dev = f"/sys/bus/pci/devices/{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        with open(dev + "/local_cpulist") as f:
+            text = f.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+        with open(dev + "/numa_node") as f:
+            return int(f.read().strip())
+    except Exception:  # noqa: BLE001
+        return None
+
+
 def run_kernels_only(args, cfg):
     """What a profiler run wants: the launches of W + K steps on rotating input sets, nothing around them."""
     from lasp_b200 import engine
@@ -294,7 +324,8 @@ def run_ours(args, cfg):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
-    torch.set_num_threads(max(1, (os.cpu_count() or 8) // world))
+    numa_node = bind_to_gpu_numa_node(local) if world > 1 else None    # before any pinned allocation
+    torch.set_num_threads(max(1, min(len(os.sched_getaffinity(0)), (os.cpu_count() or 8) // world)))
     dp = args.dp
     sp = world // dp
     if world > 1:
@@ -307,7 +338,9 @@ def run_ours(args, cfg):
     # enough independent input sets that a step never finds its inputs in L2
     set_bytes = (2 * d + 2 * e) * 2 * b * h * n
     n_sets = max(2, min(6, int(L2_BYTES * 1.6 // set_bytes) + 1))
-    sets = [make_set(cfg, 1000 * rank + i, device, dtype) for i in range(n_sets)]
+    raw_qk = args.qk != "premapped"
+    qk_scale, qk_map = qk_preprocessing(cfg) if raw_qk else (1.0, None)
+    sets = [make_set(cfg, 1000 * rank + i, device, dtype, raw=raw_qk) for i in range(n_sets)]
     for st in sets:
         for t in st[:3]:
             t.requires_grad_(True)
@@ -315,6 +348,13 @@ def run_ours(args, cfg):
     DKV = torch.empty(b, h, d, e, device=device)
 
     def operator(q, k, v):
+        if args.qk == "folded":      # the kernels preprocess q and k themselves
+            if sp > 1:
+                return lasp_b200.lasp_fuse_parallel_fused(q, k, v, s, KV, DKV, qk_scale=qk_scale, feature_map=qk_map)
+            return lasp_b200.lightning_attn_fused(q, k, v, s, qk_scale=qk_scale, feature_map=qk_map)
+        if args.qk == "torch":       # the caller preprocesses them, inside the timed region
+            from lasp_b200._core import preprocess_qk
+            q, k = preprocess_qk(q, qk_scale, qk_map), preprocess_qk(k, qk_scale, qk_map)
         return lasp_fuse_parallel(q, k, v, s, KV, DKV) if sp > 1 else lightning_attn(q, k, v, s)
 
     plan = None if wide else engine.make_plan(b, h, n, d, e, dtype)
@@ -324,12 +364,13 @@ def run_ours(args, cfg):
     if world > 1:
         from lasp_b200.utils import get_sequence_parallel_group
         group = get_sequence_parallel_group()
-    if not args.eager and not wide:
+    if not args.eager and not wide and args.qk != "torch":
         # the launches of a step go through the C ABI and are replayed from a CUDA graph, one per input set
         from lasp_b200.pipeline import FixedStep
         side = torch.cuda.Stream()
         try:
-            fixed_steps = [FixedStep(q.detach(), k.detach(), v.detach(), do, s, group) for q, k, v, do in sets]
+            fixed_steps = [FixedStep(q.detach(), k.detach(), v.detach(), do, s, group, qk_scale=qk_scale,
+                                     feature_map=qk_map) for q, k, v, do in sets]
             usable = 1
         except Exception as exc:  # noqa: BLE001  (no peer-mapped exchange here: time the eager NCCL path)
             graph_note = f"eager operator calls ({type(exc).__name__}: {exc})"[:200]
@@ -352,7 +393,7 @@ def run_ours(args, cfg):
 
     # ---- parity before anything is timed (N > 1): graph path and public operator against the oracle chain
     parity = None
-    if world > 1:
+    if world > 1 and args.qk == "premapped":
         from oracle import lasp_oracle as O
         from lasp_b200.pipeline import FixedStep
         dp_rank, sp_rank = rank // sp, rank % sp
@@ -441,7 +482,7 @@ def run_ours(args, cfg):
                  "ms_per_step": ms_sus.item() / extra}
 
     # ---- end to end through the public operator with host buffers ---------
-    host_in = make_set(cfg, 5000 + rank, device, dtype, pinned=True)
+    host_in = make_set(cfg, 5000 + rank, device, dtype, pinned=True, raw=raw_qk)
     host_out = [torch.empty_like(t).pin_memory() for t in host_in]
     h2d = sum(t.numel() * t.element_size() for t in host_in)
     d2h = sum(t.numel() * t.element_size() for t in host_out)
@@ -580,7 +621,8 @@ def run_ours(args, cfg):
         "metric": metric_name(cfg), "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": cfg["text"], "name": args.config, "parallelism": f"dp{dp}xsp{sp}",
+        "config": {"workload": cfg["text"], "name": args.config, "qk_preprocessing": args.qk,
+                   "parallelism": f"dp{dp}xsp{sp}",
                    "global_batch": b * dp, "global_seq_len": n * sp,
                    "kernel_path": "tensor (128-wide slices)" if wide else plan.path_name,
                    "launch": f"cuda graph of the {graphs[0][1].launches} C-ABI launches of a step" if graphs
@@ -590,7 +632,8 @@ def run_ours(args, cfg):
                    "l2": f"inputs rotate over {n_sets} independent sets ({n_sets * set_bytes / 1e6:.0f} MB) > L2"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_steps, "mode": e2e_mode, "serial_value": e2e_serial,
-                "pcie_gbs_per_rank": (h2d + d2h) * e2e_value / tokens_per_step / 1e9},
+                "pcie_gbs_per_rank": (h2d + d2h) * e2e_value / tokens_per_step / 1e9,
+                "host_numa_node_of_rank0": numa_node},
         "gpu_launches": launches * args.steps,
         "kernel_faults": fault_word,
         "clocks": clocks.summary(), "sustained": sustained,
@@ -618,6 +661,10 @@ def main():
     ap.add_argument("--config", default="cfg1", choices=sorted(CONFIGS))
     ap.add_argument("--dp", type=int, default=1, help="data-parallel size; sequence-parallel size = gpus / dp")
     ap.add_argument("--eager", action="store_true", help="time the public operator launch by launch (no CUDA graph)")
+    ap.add_argument("--qk", default="premapped", choices=["premapped", "folded", "torch"],
+                    help="where the configuration's preprocessing of q and k (1/sqrt(d), elu(x)+1) happens: before the "
+                         "timed region (as BASELINE words it), inside the kernels, or as torch operations of the caller "
+                         "inside the timed region")
     ap.add_argument("--kernels-only", action="store_true",
                     help="W + K steps of the C-ABI launches on one GPU and nothing else (the target of profiler runs)")
     args = ap.parse_args()

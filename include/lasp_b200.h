@@ -37,7 +37,7 @@
 extern "C" {
 #endif
 
-#define LASP_B200_ABI_VERSION 2
+#define LASP_B200_ABI_VERSION 3
 
 /* the library is built with hidden visibility; only the entry points below are exported */
 #if defined(__GNUC__)
@@ -68,11 +68,21 @@ typedef enum {
   LASP_PATH_TENSOR = 2  /* tcgen05/TMEM/TMA kernels: bf16, d,e in {64,128}, n >= 128 (a ragged tail is fine) */
 } lasp_path;
 
+/* Preprocessing of q and k folded into the kernels' load path: the operator is evaluated on
+ * qk_scale * map(q) and qk_scale * map(k), and dq, dk are the gradients with respect to the RAW q and k
+ * (chain rule applied in the epilogues).  Replaces the caller-side passes `q, k = elu(q) + 1, elu(k) + 1`
+ * and `q, k *= d ** -0.5` in front of lightning_attn / lasp_* (lasp/lightning_attention.py:510); each of
+ * them would read and write q and k once more in an operator bound by memory traffic.  Only the fused
+ * tensor-core launches (forward, backward, the linked forms, bwd_dq, bwd_dkv) take it; every other entry
+ * point returns LASP_ERR_PATH when it is requested. */
+typedef enum { LASP_QK_IDENTITY = 0, LASP_QK_ELU1 = 1 /* elu(x) + 1 */ } lasp_qk_map;
+
 typedef struct {
   int32_t b, h, n, d, e;
-  int32_t dtype;  /* lasp_dtype of q,k,v,o,do,dq,dk,dv */
-  int32_t path;   /* lasp_path */
-  int32_t reserved;
+  int32_t dtype;   /* lasp_dtype of q,k,v,o,do,dq,dk,dv */
+  int32_t path;    /* lasp_path */
+  int32_t qk_map;  /* lasp_qk_map */
+  float qk_scale;  /* 0 is read as 1 */
 } lasp_problem;
 
 /* Forward arguments.  ws = workspace of lasp_b200_fwd_workspace_bytes(); after

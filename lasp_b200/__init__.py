@@ -8,6 +8,8 @@ from .lasp_fuse_parallel import lasp_fuse_parallel, lasp_fuse_parallel_  # noqa:
 from .lasp_naive import lasp_naive, lasp_naive_  # noqa: F401
 from .lightning_attention import lightning_attn, lightning_attn_  # noqa: F401
 from .utils import *  # noqa: F401,F403
+from ._core import lightning_attn_fused  # noqa: F401
+from ._core import sequence_parallel_fused as lasp_fuse_parallel_fused  # noqa: F401
 
 
 def check_faults(clear: bool = True) -> None:

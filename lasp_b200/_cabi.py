@@ -10,7 +10,7 @@ import ctypes as C
 import os
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "liblasp_b200.so")
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 # lasp_dtype / lasp_path / lasp_status of include/lasp_b200.h
 F32, BF16, F16 = 0, 1, 2
@@ -31,8 +31,11 @@ class LaspStatusError(RuntimeError):
         self.status = status
 
 
-class Problem(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in ("b", "h", "n", "d", "e", "dtype", "path", "reserved")]
+class Problem(C.Structure):   # lasp_problem
+    _fields_ = [(n, C.c_int32) for n in ("b", "h", "n", "d", "e", "dtype", "path", "qk_map")] + [("qk_scale", C.c_float)]
+
+
+QK_MAPS = {None: 0, "identity": 0, "elu1": 1}   # lasp_qk_map
 
 
 class FwdArgs(C.Structure):

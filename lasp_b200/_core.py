@@ -72,9 +72,32 @@ def sliced_apply(fn, q, k, v, state_bufs=()):
     return outs[0] if len(outs) == 1 else torch.cat(outs, dim=-1)
 
 
-def _plan_for(q, v, path=None):
+def _plan_for(q, v, path=None, qk_scale=1.0, feature_map=None):
     b, h, n, d = q.shape
-    return ENGINE.make_plan(b, h, n, d, v.shape[-1], q.dtype, path)
+    if qk_scale == 1.0 and feature_map is None:
+        return ENGINE.make_plan(b, h, n, d, v.shape[-1], q.dtype, path)
+    return ENGINE.make_plan(b, h, n, d, v.shape[-1], q.dtype, path, qk_scale=qk_scale, feature_map=feature_map)
+
+
+def preprocess_qk(x, qk_scale=1.0, feature_map=None):
+    """qk_scale * map(x) with torch operations: what a caller of the reference writes in front of the operator,
+    and what the ``*_fused`` operators do themselves when the kernels of a problem cannot take it over."""
+    if feature_map == "elu1":
+        x = torch.nn.functional.elu(x) + 1.0
+    elif feature_map is not None:
+        raise ValueError(f"unknown feature map {feature_map!r}; use None or 'elu1'")
+    return x if qk_scale == 1.0 else x * qk_scale
+
+
+def kernels_preprocess(q, v, qk_scale, feature_map) -> bool:
+    """True when the kernels that will run this (slice of a) problem fold qk_scale * map(.) into their loads."""
+    if not q.is_cuda:
+        return False
+    try:
+        _plan_for(q, v, qk_scale=qk_scale, feature_map=feature_map)
+    except ENGINE.LaspStatusError:
+        return False
+    return True
 
 
 def _check_shapes(q, k, v, s):
@@ -100,10 +123,10 @@ class LightningAttention(torch.autograd.Function):
     lasp/lightning_attention.py:396-504; gradients for q, k, v only."""
 
     @staticmethod
-    def forward(ctx, q, k, v, s):
+    def forward(ctx, q, k, v, s, qk_scale=1.0, feature_map=None):
         _check_shapes(q, k, v, s)
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        plan = _plan_for(q, v)
+        plan = _plan_for(q, v, qk_scale=qk_scale, feature_map=feature_map)
         fw = ENGINE.Forward(plan, q, k, v, s)
         o = fw.run()
         ctx.plan = plan
@@ -116,7 +139,7 @@ class LightningAttention(torch.autograd.Function):
         q, k, v, s = ctx.saved_tensors
         bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws)
         dq, dk, dv = bw.run()
-        return dq, dk, dv, None
+        return dq, dk, dv, None, None, None
 
 
 class SequenceParallelAttention(torch.autograd.Function):
@@ -143,7 +166,7 @@ class SequenceParallelAttention(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, q, k, v, s, KV, DKV, overlap):
+    def forward(ctx, q, k, v, s, KV, DKV, overlap, qk_scale=1.0, feature_map=None):
         _check_shapes(q, k, v, s)
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         b, h, n, d = q.shape
@@ -156,7 +179,7 @@ class SequenceParallelAttention(torch.autograd.Function):
         last = get_sequence_parallel_world_size() - 1
         prev_rank, next_rank = get_seq_parallel_send_rank(), get_seq_parallel_receive_rank()
         link = comm.StateLink(group)
-        plan = _plan_for(q, v)
+        plan = _plan_for(q, v, qk_scale=qk_scale, feature_map=feature_map)
         kv_in = KV if rank > 0 else None
         exchange = comm.relay_for(group, KV.numel(), q.device) if (overlap and last > 0 and q.is_cuda) else None
 
@@ -216,7 +239,7 @@ class SequenceParallelAttention(torch.autograd.Function):
                 ctx.exchange.exchange_scan(ctx.plan, bw.ws, s, backward=True, phase="gather")
                 bw.dkv_after_scan()
             ENGINE.fault_watch(q.device).arm(q.device)   # looked at when the next call starts
-            return bw.dq, bw.dk, bw.dv, None, None, None, None
+            return bw.dq, bw.dk, bw.dv, None, None, None, None, None, None
         bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws, dkv_in=dkv_in,
                              dkv_out=DKV if rank > 0 else None)
         if ctx.overlap:
@@ -233,9 +256,44 @@ class SequenceParallelAttention(torch.autograd.Function):
             bw.run()
             if rank > 0:
                 link.send(DKV, ctx.prev_rank)
-        return bw.dq, bw.dk, bw.dv, None, None, None, None
+        return bw.dq, bw.dk, bw.dv, None, None, None, None, None, None
 
 
 def sequence_parallel(q, k, v, s, KV, DKV, overlap: bool):
     return sliced_apply(lambda qs, ks, vs, kv, dkv: SequenceParallelAttention.apply(qs, ks, vs, s, kv, dkv, overlap),
+                        q, k, v, (KV, DKV))
+
+
+def _slice_like(q, v):
+    """The widest slice `sliced_apply` will hand to the kernels for these head dimensions."""
+    return q[..., :MAX_HEAD_SLICE], v[..., :MAX_HEAD_SLICE]
+
+
+def lightning_attn_fused(q, k, v, s, qk_scale: float = 1.0, feature_map=None):
+    """``lightning_attn(c * map(q), c * map(k), v, s)`` with the preprocessing of q and k folded into the
+    kernels' load path (and its chain rule into their epilogues): q and k are read once, nothing is written in
+    between.  ``feature_map``: None or "elu1" (elu(x) + 1); ``qk_scale``: c.  Problems whose kernels cannot
+    do this (fp32 path, head dims other than 64 / 128 per slice, more spans than SMs) get the same result from
+    torch operations in front of the operator."""
+    if (qk_scale == 1.0 and feature_map is None) or not kernels_preprocess(*_slice_like(q, v), qk_scale, feature_map):
+        return sliced_apply(lambda qs, ks, vs: LightningAttention.apply(qs, ks, vs, s),
+                            preprocess_qk(q, qk_scale, feature_map), preprocess_qk(k, qk_scale, feature_map), v)
+    return sliced_apply(lambda qs, ks, vs: LightningAttention.apply(qs, ks, vs, s, qk_scale, feature_map), q, k, v)
+
+
+def sequence_parallel_fused(q, k, v, s, KV, DKV, qk_scale: float = 1.0, feature_map=None):
+    """``lasp_fuse_parallel`` on c * map(q), c * map(k) with the preprocessing inside the kernels where the
+    rank's launches are the fused ones that hand the state over themselves; torch operations otherwise."""
+    qs, vs = _slice_like(q, v)
+    in_kernel = (qk_scale != 1.0 or feature_map is not None) and kernels_preprocess(qs, vs, qk_scale, feature_map)
+    if in_kernel and get_sequence_parallel_world_size() > 1:
+        b, h, n, d = qs.shape
+        plan = _plan_for(qs, vs, qk_scale=qk_scale, feature_map=feature_map)
+        relay = comm.relay_for(get_sequence_parallel_group(), b * h * d * vs.shape[-1], q.device)
+        in_kernel = relay is not None and ENGINE.linked_ok(plan)
+    if not in_kernel:
+        return sequence_parallel(preprocess_qk(q, qk_scale, feature_map), preprocess_qk(k, qk_scale, feature_map), v, s,
+                                 KV, DKV, True)
+    return sliced_apply(lambda qs_, ks_, vs_, kv, dkv: SequenceParallelAttention.apply(qs_, ks_, vs_, s, kv, dkv, True,
+                                                                                       qk_scale, feature_map),
                         q, k, v, (KV, DKV))

@@ -82,6 +82,9 @@ int make_dims(const lasp_problem* p, lasp::Dims* m) {
   if ((long long)p->b * p->h > 65535) return LASP_ERR_SHAPE;
   m->b = p->b; m->h = p->h; m->n = p->n; m->d = p->d; m->e = p->e;
   m->dtype = p->dtype;
+  if (p->qk_map != LASP_QK_IDENTITY && p->qk_map != LASP_QK_ELU1) return LASP_ERR_SHAPE;
+  m->qk_map = p->qk_map;
+  m->qk_scale = p->qk_scale == 0.f ? 1.f : p->qk_scale;
   m->walk = 0;
   m->tiles = (p->n + lasp::kTensorTile - 1) / lasp::kTensorTile;
   m->span = 1;
@@ -92,6 +95,7 @@ int make_dims(const lasp_problem* p, lasp::Dims* m) {
   if (path != LASP_PATH_TENSOR && path != LASP_PATH_SIMT) return LASP_ERR_PATH;
   m->path = path;
   if (path == LASP_PATH_SIMT) {
+    if (lasp::has_qk_preprocessing(*m)) return LASP_ERR_PATH;   // folded into the tensor-core kernels only
     m->chunk = lasp::kSimtChunk;
     m->nc = (p->n + m->chunk - 1) / m->chunk;
     return LASP_OK;
@@ -108,6 +112,10 @@ int make_dims(const lasp_problem* p, lasp::Dims* m) {
   m->span = span;
   m->chunk = span * lasp::kTensorTile;
   m->nc = (m->tiles + span - 1) / span;
+  // the q,k preprocessing lives in the fused launches (and the dQ walk): not in the phase-by-phase schedule
+  if (lasp::has_qk_preprocessing(*m) &&
+      (unfused_requested() || (m->nc > 1 && p->b * p->h * m->nc > lasp::sm_count())))
+    return LASP_ERR_PATH;
   return LASP_OK;
 }
 
@@ -197,16 +205,19 @@ size_t lasp_b200_bwd_workspace_bytes(const lasp_problem* p) { return lasp_b200_f
 namespace {
 
 int fwd_chunk_states(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs) {
+  if (lasp::has_qk_preprocessing(m)) return LASP_ERR_PATH;
   if (m.walk) return cuda_fail(lasp::walk_span_totals(m, a->k, a->v, a->s, lasp::ws_local(a->ws, m), false, cs));
   return cuda_fail(lasp::simt_chunk_states(m, a->k, a->v, a->s, lasp::ws_local(a->ws, m), false, cs));
 }
 
 int fwd_scan(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs) {
+  if (lasp::has_qk_preprocessing(m)) return LASP_ERR_PATH;
   return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_local(a->ws, m), lasp::ws_prefix(a->ws, m), a->kv_in, a->kv_out,
                                      false, cs));
 }
 
 int fwd_output(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs) {
+  if (lasp::has_qk_preprocessing(m)) return LASP_ERR_PATH;
   if (m.walk)
     return cuda_fail(lasp::walk_fwd_output(m, a->q, a->k, a->v, a->s, lasp::ws_walk_border(a->ws, m),
                                            lasp::ws_walk_sync(a->ws), a->o, cs));
@@ -214,19 +225,22 @@ int fwd_output(const lasp::Dims& m, const lasp_fwd_args* a, cudaStream_t cs) {
 }
 
 int bwd_chunk_states(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs) {
+  if (lasp::has_qk_preprocessing(m)) return LASP_ERR_PATH;
   if (m.walk) return cuda_fail(lasp::walk_span_totals(m, a->q, a->d_o, a->s, lasp::ws_local(a->ws, m), true, cs));
   return cuda_fail(lasp::simt_chunk_states(m, a->q, a->d_o, a->s, lasp::ws_local(a->ws, m), true, cs));
 }
 
 int bwd_scan(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs) {
+  if (lasp::has_qk_preprocessing(m)) return LASP_ERR_PATH;
   return cuda_fail(lasp::scan_states(m, a->s, lasp::ws_local(a->ws, m), lasp::ws_prefix(a->ws, m), a->dkv_in,
                                      a->dkv_out, true, cs));
 }
 
 int bwd_grads(const lasp::Dims& m, const lasp_bwd_args* a, cudaStream_t cs) {
+  if (lasp::has_qk_preprocessing(m)) return LASP_ERR_PATH;
   if (m.walk) {
     // dQ walks forward over the border states the forward pass left in its workspace; dK, dV walk backward
-    int st = cuda_fail(lasp::walk_bwd_dq(m, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m),
+    int st = cuda_fail(lasp::walk_bwd_dq(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m),
                                           lasp::ws_walk_sync(a->fwd_ws), a->dq, cs));
     if (st != LASP_OK) return st;
     return cuda_fail(lasp::walk_bwd_dkv(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->ws, m), a->dk,
@@ -298,7 +312,7 @@ int lasp_b200_bwd_dq(const lasp_problem* p, const lasp_bwd_args* a, void* stream
   lasp::Dims m;
   int st = check_bwd(p, a, &m, true);
   if (st != LASP_OK || !m.walk) return st;
-  return cuda_fail(lasp::walk_bwd_dq(m, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m),
+  return cuda_fail(lasp::walk_bwd_dq(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m),
                                           lasp::ws_walk_sync(a->fwd_ws), a->dq,
                                      static_cast<cudaStream_t>(stream)));
 }
@@ -309,6 +323,7 @@ int lasp_b200_bwd_dkv_walk(const lasp_problem* p, const lasp_bwd_args* a, void* 
   if (st != LASP_OK) return st;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (!m.walk) return bwd_grads(m, a, cs);
+  if (lasp::has_qk_preprocessing(m)) return LASP_ERR_PATH;
   return cuda_fail(lasp::walk_bwd_dkv(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->ws, m), a->dk, a->dv,
                                       cs));
 }
@@ -330,7 +345,7 @@ int lasp_b200_backward(const lasp_problem* p, const lasp_bwd_args* a, void* stre
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (fusable(m)) {
     // dQ walks forward over the border states the forward pass kept; dK, dV walk backward in one fused launch
-    if ((st = cuda_fail(lasp::walk_bwd_dq(m, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m),
+    if ((st = cuda_fail(lasp::walk_bwd_dq(m, a->q, a->k, a->v, a->d_o, a->s, lasp::ws_walk_border(a->fwd_ws, m),
                                           lasp::ws_walk_sync(a->fwd_ws), a->dq,
                                           cs))) != LASP_OK)
       return st;

@@ -35,7 +35,11 @@ struct Dims {
   int walk;   // 1 on the tensor path: the state is carried on chip along a span of tiles
   int tiles;  // tensor path: 128-token tiles per sequence
   int span;   // tensor path: tiles per span (chunk = span * 128)
+  int qk_map;      // q and k enter as qk_scale * map(x): 0 identity, 1 elu(x) + 1
+  float qk_scale;  // (1 when the caller left it 0)
 };
+
+inline bool has_qk_preprocessing(const Dims& m) { return m.qk_map != 0 || m.qk_scale != 1.f; }
 
 // SM count of the current device (cached per device ordinal)
 int sm_count();
@@ -113,7 +117,7 @@ cudaError_t walk_fwd_output(const Dims& m, const void* q, const void* k, const v
 cudaError_t walk_fwd_fused(const Dims& m, const void* q, const void* k, const void* v, const float* s,
                            const float* x_in, float* x_out, uint32_t* sync, float* totals, float* prefix, void* o,
                            const lasp_exchange_args* link, cudaStream_t st);
-cudaError_t walk_bwd_dq(const Dims& m, const void* k, const void* v, const void* d_o, const float* s,
+cudaError_t walk_bwd_dq(const Dims& m, const void* q, const void* k, const void* v, const void* d_o, const float* s,
                         const float* prefix, const uint32_t* fwd_sync, void* dq, cudaStream_t st);
 cudaError_t walk_bwd_dkv(const Dims& m, const void* q, const void* k, const void* v, const void* d_o,
                          const float* s, const float* suffix, void* dk, void* dv, cudaStream_t st);

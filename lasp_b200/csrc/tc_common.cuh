@@ -77,8 +77,9 @@ __device__ __forceinline__ void stage_row32(uint32_t taddr1, uint32_t taddr2, fl
 // leftwards by repeated multiplication with lambda (short independent chains), so it can only
 // underflow towards the far columns.  The 32 rows of a warp are `row0 .. row0+31`: groups wholly
 // below the diagonal for every row of the warp need no comparisons, groups wholly above it are zero.
+// `pre` multiplies every element (the folded q,k scale).
 __device__ __forceinline__ void masked_store32(uint32_t taddr, uint8_t* tile, int row, int col0, float sl2,
-                                               float lam) {
+                                               float lam, float pre = 1.f) {
   const int row0 = row & ~31;
   if (col0 > row0 + 31) {   // the whole block is above the diagonal (same for every lane of the warp)
 #pragma unroll
@@ -90,7 +91,7 @@ __device__ __forceinline__ void masked_store32(uint32_t taddr, uint8_t* tile, in
   tmem_ld32(taddr, r);
   float f[4];
 #pragma unroll
-  for (int g = 0; g < 4; ++g) f[g] = decay_pow(sl2, row - min(row, col0 + 8 * g + 7));
+  for (int g = 0; g < 4; ++g) f[g] = pre * decay_pow(sl2, row - min(row, col0 + 8 * g + 7));
   tmem_ld_wait();
   if (col0 + 31 <= row0) {  // the whole block is below the diagonal
 #pragma unroll
@@ -126,7 +127,7 @@ __device__ __forceinline__ void masked_store32(uint32_t taddr, uint8_t* tile, in
 // TRANSPOSED = true : lane = key c, column = query row r:  [r >= c] lambda^(r-c)   (the tile is S^T)
 template <bool TRANSPOSED>
 __device__ __forceinline__ void masked_pack32(uint32_t src, int row, int col0, float sl2, float lam,
-                                              uint32_t (&out)[16]) {
+                                              uint32_t (&out)[16], float pre = 1.f) {
   const int row0 = row & ~31;
   const bool none = TRANSPOSED ? (col0 + 31 < row0) : (col0 > row0 + 31);   // same for every lane of the warp
   if (none) {
@@ -141,7 +142,7 @@ __device__ __forceinline__ void masked_pack32(uint32_t src, int row, int col0, f
   for (int g = 0; g < 4; ++g) {
     // the chain of a group of eight columns starts at its live column nearest the diagonal
     const int start = TRANSPOSED ? max(row, col0 + 8 * g) : min(row, col0 + 8 * g + 7);
-    f[g] = decay_pow(sl2, TRANSPOSED ? start - row : row - start);
+    f[g] = pre * decay_pow(sl2, TRANSPOSED ? start - row : row - start);
   }
   tmem_ld_wait();
   const bool all = TRANSPOSED ? (col0 >= row0 + 31) : (col0 + 31 <= row0);
@@ -161,10 +162,32 @@ __device__ __forceinline__ void masked_pack32(uint32_t src, int row, int col0, f
   }
 }
 
+// exp of a pair of bf16 values: the argument is scaled in fp32, the exponential itself is ONE special-function
+// operation for the pair (the map passes are bound by that unit)
+__device__ __forceinline__ __nv_bfloat162 exp_bf16x2(uint32_t u) {
+  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
+  const uint32_t t = pack_bf16(f.x * kLog2e, f.y * kLog2e);
+  uint32_t r;
+  asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(r) : "r"(t));
+  return *reinterpret_cast<__nv_bfloat162*>(&r);
+}
+// elu(x) + 1 on a pair of bf16 values (the feature map of the no-decay linear-transformer configuration):
+// x + 1 for x > 0, exp(x) otherwise = max(x, 0) + min(exp(x), 1), without a branch
+__device__ __forceinline__ uint32_t elu1_bf16x2(uint32_t u) {
+  const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&u);
+  const __nv_bfloat162 r = __hadd2(__hmax2(x, __float2bfloat162_rn(0.f)), __hmin2(exp_bf16x2(u), __float2bfloat162_rn(1.f)));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+// its derivative: 1 for x > 0, exp(x) otherwise = min(exp(x), 1)
+__device__ __forceinline__ float2 elu1_slope_bf16x2(uint32_t u) {
+  return __bfloat1622float2(__hmin2(exp_bf16x2(u), __float2bfloat162_rn(1.f)));
+}
+
 // Multiplies CHUNKS 16-byte pieces of row `row` of a swizzled tile of C rows by w, in place, starting
 // at piece `first` (pieces are counted slab by slab; a row keeps its pieces under the swizzle, so the
 // physical position inside the row does not matter).  `lane` rotates the order to spread the banks.
-template <int CHUNKS>
+// MAP: each element goes through elu(x) + 1 first.
+template <int CHUNKS, bool MAP = false>
 __device__ __forceinline__ void scale_row_pieces(uint8_t* tile, int row, int first, float w, int lane) {
   static_assert((CHUNKS & (CHUNKS - 1)) == 0, "a power of two");
   uint4 v[CHUNKS];
@@ -180,10 +203,44 @@ __device__ __forceinline__ void scale_row_pieces(uint8_t* tile, int row, int fir
     uint32_t* u = reinterpret_cast<uint32_t*>(&v[q]);
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
-      const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u[t]));
-      u[t] = pack_bf16(f.x * w, f.y * w);
+      if (MAP) u[t] = elu1_bf16x2(u[t]);
+      if (!MAP || w != 1.f) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u[t]));
+        u[t] = pack_bf16(f.x * w, f.y * w);
+      }
     }
     *p[q] = v[q];
+  }
+}
+
+// stage_row32 with the chain rule of the folded q,k preprocessing x' = c * map(x): the 32 accumulator values
+// (a gradient with respect to x') are multiplied by c * map'(x) on their way to the staging tile, x read from
+// the raw tensor (`raw` points at column 0 of this thread's row).
+__device__ __forceinline__ void stage_row32_chain(uint32_t taddr, uint8_t* tile, int row, int col0,
+                                                  const __nv_bfloat16* raw, float c, bool elu) {
+  uint4 x[4];
+  if (elu) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[j] = __ldg(reinterpret_cast<const uint4*>(raw + col0) + j);
+  }
+  uint32_t a[32];
+  tmem_ld32(taddr, a);
+  tmem_ld_wait();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float m[8];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      float sx = c, sy = c;
+      if (elu) {
+        const float2 sl = elu1_slope_bf16x2(reinterpret_cast<const uint32_t*>(&x[j])[t]);
+        sx *= sl.x, sy *= sl.y;
+      }
+      m[2 * t] = __uint_as_float(a[8 * j + 2 * t]) * sx;
+      m[2 * t + 1] = __uint_as_float(a[8 * j + 2 * t + 1]) * sy;
+    }
+    *reinterpret_cast<uint4*>(tile + tile_offset(row, col0 + 8 * j, C)) =
+        make_uint4(pack_bf16(m[0], m[1]), pack_bf16(m[2], m[3]), pack_bf16(m[4], m[5]), pack_bf16(m[6], m[7]));
   }
 }
 

@@ -386,6 +386,9 @@ struct WalkArgs {
   const float* x_in;   // fused: incoming rank state (b,h,d,e) or NULL
   float* x_out;        // fused: outgoing rank state (b,h,d,e) or NULL
   int h, n, tiles, span, nspans, items;
+  float qk_scale;      // q and k enter as qk_scale * map(q), qk_scale * map(k)
+  int elu;             // map = elu(x) + 1 (otherwise the identity)
+  const void* raw;     // backward with a map or a scale: the raw q (dQ walk) or k (dK/dV walk) for the chain rule
   int even;            // the tiles of a sequence are shared out evenly among its spans (see TileWalk); a fused
                        // forward records it in sync[kSyncEven], the dQ walk reads it from the forward's workspace
   const uint32_t* even_word;   // dQ: where the forward pass recorded how it cut the sequences (NULL: a.even)
@@ -437,7 +440,7 @@ __device__ __forceinline__ void write_state_operand(uint8_t* tile, int rows, int
 //   are read again by the walk (they are in L2 by then).  The last span of a sequence needs no total
 //   unless a.all_totals; the outgoing rank state is the state after the last tile of the last span.
 // ---------------------------------------------------------------------------
-template <int D, int E, bool DQ, bool FUSED>
+template <int D, int E, bool DQ, bool FUSED, bool PRE, bool LINK>
 __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUtensorMap map_x,
                                                      const __grid_constant__ CUtensorMap map_y,
                                                      const __grid_constant__ CUtensorMap map_z,
@@ -455,6 +458,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
   uint8_t* sp = smem + 6 * kBuf;
   __shared__ uint64_t x_full[2], y_full[2], z_full[2], s_full[2], sm_ready[2], o_full[2], o2_full[2], staged[2];
   __shared__ uint64_t p_ready, l_free, o_free, ys_ready, o2s_ready, l_full;
+  __shared__ uint64_t mapped[2];   // with a feature map: the workers have mapped the tile's X, Y (dQ: Z) in place
   __shared__ uint64_t ring_full[2], ring_scaled[2], ring_empty[2], sum_done;   // the span-total phase
   __shared__ uint32_t tmem_slot, step_s, step_x, even_s;
   __shared__ int dead;
@@ -472,6 +476,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       mbar_init(&o_full[p], 1);
       mbar_init(&o2_full[p], 1);
       mbar_init(&staged[p], kWorkers);
+      mbar_init(&mapped[p], kWorkers);
       mbar_init(&ring_full[p], 1);
       mbar_init(&ring_scaled[p], kWorkers);
       mbar_init(&ring_empty[p], 1);
@@ -490,7 +495,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
     prefetch_tensormap(&map_out);
     if constexpr (FUSED) {
       step_s = a.coop ? ld_volatile_u32(a.sync) + 1 : 0;                       // this launch among those on the workspace
-      step_x = a.link.ranks > 0 ? ld_volatile_u32(a.link.counters) + 1 : 0;    // this hand-over in the group
+      step_x = LINK && a.link.ranks > 0 ? ld_volatile_u32(a.link.counters) + 1 : 0;    // this hand-over in the group
     }
   }
   if (warp == 2) tmem_alloc(&tmem_slot, 512);
@@ -588,9 +593,11 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
         umma_gemm(t_s[q], Operand{smem_u32(sx[q]), C, false}, Operand{smem_u32(sy[q]), C, false}, C, WX / 16, false);
         umma_commit(&s_full[q]);
       };
+      const bool map_xy = PRE && a.elu && !DQ, map_z = PRE && a.elu && DQ;
       if (total > 0) {
         wait_or_fault(&x_full[0], 0, &dead, fault, kFaultTmaWait);
         wait_or_fault(&y_full[0], 0, &dead, fault, kFaultTmaWait);
+        if (map_xy) wait_or_fault(&mapped[0], 0, &dead, fault, kFaultMmaWait);
         issue_s(0);
       }
       for (int i = 0; i < total; ++i) {
@@ -603,7 +610,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
           // O1 = S_m Z on top of the row-scaled O2, the masked scores read from tensor memory.  It goes out
           // after L: the commit behind it then also covers L's reads of Y and Z, which is what frees them
           if (need_o1 && !need_o2 && !need_l && mbar_test_wait(&sm_ready[p], ph) && mbar_test_wait(&o2s_ready, one) &&
-              mbar_test_wait(&z_full[p], ph)) {
+              mbar_test_wait(&z_full[p], ph) && (!map_z || mbar_test_wait(&mapped[p], ph))) {
             TRACE(32 + i * 5 + 3);
             tc_fence_after_sync();
             umma_gemm_ts(t_o, t_s[p], true, Operand{smem_u32(sz[p]), C, true}, WZ, true);
@@ -613,7 +620,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
           }
           // L = K^T diag(w) V (d x e), the scaled rows being Y's; the state update has read the previous L
           if (need_l && mbar_test_wait(&ys_ready, one) && mbar_test_wait(&z_full[p], ph) &&
-              (i < 1 || mbar_test_wait(&l_free, one ^ 1))) {
+              (!map_z || mbar_test_wait(&mapped[p], ph)) && (i < 1 || mbar_test_wait(&l_free, one ^ 1))) {
             TRACE(32 + i * 5 + 1);
             tc_fence_after_sync();
             if constexpr (!DQ)
@@ -638,7 +645,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
           }
           // S of the next tile; S[q] held the masked scores of tile i-1: its O1 must have read them
           if (need_s && mbar_test_wait(&x_full[q], uq & 1) && mbar_test_wait(&y_full[q], uq & 1) &&
-              (i + 1 < 2 || mbar_test_wait(&o_full[q], (uq - 1) & 1))) {
+              (!map_xy || mbar_test_wait(&mapped[q], uq & 1)) && (i + 1 < 2 || mbar_test_wait(&o_full[q], (uq - 1) & 1))) {
             TRACE(32 + i * 5 + 2);
             issue_s(i + 1);
             need_s = false;
@@ -659,6 +666,27 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
     constexpr int kHalfE = E / 2;
     float P[kHalfE];  // this thread's part of the state: row `row`, columns [half * E/2, (half+1) * E/2)
     float sl2 = 0.f, lam = 1.f;
+    // q and k enter as c * map(q), c * map(k): the map is applied to the tiles in shared memory, c is folded
+    // into factors that exist anyway (dQ: the state already carries k's c)
+    // (PRE = false: instantiations without any of this, for callers who bring q and k as they are)
+    const float c = PRE ? a.qk_scale : 1.f;
+    const float c_mask = DQ ? c : c * c, c_o2 = DQ ? 1.f : c;
+    const bool elu = PRE && a.elu != 0;
+    // brings tile j (buffers of parity j & 1) through the feature map once its loads have landed
+    auto map_tile = [&](int j) {
+      const int q = j & 1, uq = (j >> 1) & 1;
+      if constexpr (!DQ) {
+        wait_or_fault(&x_full[q], uq, &dead, fault, kFaultTmaWait);
+        wait_or_fault(&y_full[q], uq, &dead, fault, kFaultTmaWait);
+        scale_row_pieces<WX / 16, true>(sx[q], row, half * (WX / 16), 1.f, lane);
+        scale_row_pieces<WX / 16, true>(sy[q], row, half * (WX / 16), 1.f, lane);
+      } else {
+        wait_or_fault(&z_full[q], uq, &dead, fault, kFaultTmaWait);
+        scale_row_pieces<WZ / 16, true>(sz[q], row, half * (WZ / 16), 1.f, lane);
+      }
+      fence_async_smem();
+      mbar_arrive(&mapped[q]);
+    };
     if (sums) {
       // ---- this span's total, written where the CTAs of the later spans find it
       sl2 = a.s[my_bh % a.h] * kLog2e;
@@ -666,7 +694,11 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       for (int t = sum_t0, g = 0; t < sum_t1; ++t, ++g) {
         const int j = g & 1;
         wait_or_fault(&ring_full[j], (g >> 1) & 1, &dead, fault, kFaultTmaWait);
-        scale_row_pieces<WX / 16>(sy[j], row, half * (WX / 16), decay_pow(sl2, max(span_end - (t * C + row), 0)), lane);
+        const float wt = c * decay_pow(sl2, max(span_end - (t * C + row), 0));
+        if (elu)
+          scale_row_pieces<WX / 16, true>(sy[j], row, half * (WX / 16), wt, lane);
+        else
+          scale_row_pieces<WX / 16>(sy[j], row, half * (WX / 16), wt, lane);
         fence_async_smem();
         mbar_arrive(&ring_scaled[j]);
       }
@@ -690,6 +722,11 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       }
       if (tid == 64) TRACE(60);
     }
+    int total = 0;
+    if (elu) {
+      for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next()) ++total;
+      if (total > 0) map_tile(0);
+    }
     int i = 0;
     for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++i) {
       const int p = i & 1, ph = (i >> 1) & 1, one = i & 1;
@@ -704,7 +741,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       if (tid == 64) TRACE(1 + i * 6 + 1);
       tc_fence_after_sync();
       // state chain first: scale Y's rows so that L can run under the mask
-      scale_row_pieces<WX / 16>(sy[p], row, half * (WX / 16), decay_pow(sl2, max(len - row, 0)), lane);
+      scale_row_pieces<WX / 16>(sy[p], row, half * (WX / 16), c * decay_pow(sl2, max(len - row, 0)), lane);
       fence_async_smem();
       mbar_arrive(&ys_ready);
       if (tid == 64) TRACE(1 + i * 6 + 2);
@@ -712,13 +749,14 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         uint32_t packed[16];
-        masked_pack32<false>(t_s[p] + lane_base + half * 64 + cc * 32, row, half * 64 + cc * 32, sl2, lam, packed);
+        masked_pack32<false>(t_s[p] + lane_base + half * 64 + cc * 32, row, half * 64 + cc * 32, sl2, lam, packed, c_mask);
         tmem_st16(t_s[p] + lane_base + half * 64 + cc * 16, packed);
       }
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&sm_ready[p]);
       if (tid == 64) TRACE(1 + i * 6 + 3);
+      if (elu && i + 1 < total) map_tile(i + 1);   // the next tile's S can then go out under this tile's work
       if (w.first_of_item()) {
         // the state at the span border (the score work above does not need it, so the wait for the other
         // CTAs' totals hides behind it); the O2 MMA that read the operand tile of the previous item has completed
@@ -754,7 +792,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
                                    decay_pow(sl2, (w.t0 - w.span_t0(j + 1)) * C), P);
           }
           if (tid == 64) TRACE(61);
-          if (a.link.ranks > 0) {
+          if (LINK && a.link.ranks > 0) {
             // hand-over of the rank state inside the launch.  P holds the local part of the border state.
             const float sn = a.s[w.bh % a.h] * (float)a.n;
             const long long elems = (long long)(a.items / a.nspans) * D * E;
@@ -820,7 +858,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       wait_or_fault(&o2_full[p], ph, &dead, fault, kFaultMmaWait);
       tc_fence_after_sync();
       {
-        const float qd = decay_pow(sl2, row);
+        const float qd = c_o2 * decay_pow(sl2, row);
 #pragma unroll
         for (int cc = 0; cc < WZ / 64; ++cc) scale_tmem32(t_o + lane_base + half * (WZ / 2) + cc * 32, qd);
       }
@@ -859,10 +897,22 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       // epilogue: OUT staged in Y's buffer (the L MMA has read the scaled rows)
       wait_or_fault(&o_full[p], ph, &dead, fault, kFaultMmaWait);
       tc_fence_after_sync();
+      if (DQ && (elu || c != 1.f)) {
+        // dq = dq' * c * map'(q), q read from the raw tensor (rows past the end of the sequence are not stored)
+        const bool live = row < len;
+        const __nv_bfloat16* raw =
+            static_cast<const __nv_bfloat16*>(a.raw) + ((size_t)w.bh * a.n + (size_t)w.t * C + (live ? row : 0)) * WZ;
 #pragma unroll
-      for (int cc = 0; cc < WZ / 64; ++cc) {
-        const int col0 = half * (WZ / 2) + cc * 32;
-        stage_row32(t_o + lane_base + col0, kNoAcc, 0.f, sy[p], row, col0);
+        for (int cc = 0; cc < WZ / 64; ++cc) {
+          const int col0 = half * (WZ / 2) + cc * 32;
+          stage_row32_chain(t_o + lane_base + col0, sy[p], row, col0, raw, c, elu && live);
+        }
+      } else {
+#pragma unroll
+        for (int cc = 0; cc < WZ / 64; ++cc) {
+          const int col0 = half * (WZ / 2) + cc * 32;
+          stage_row32(t_o + lane_base + col0, kNoAcc, 0.f, sy[p], row, col0);
+        }
       }
       tc_fence_before_sync();
       mbar_arrive(&o_free);
@@ -889,7 +939,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
         st_volatile_u32(a.sync + 1, 0u);
         __threadfence();
         st_volatile_u32(a.sync, step_s);
-        if (a.link.ranks > 0) {
+        if (LINK && a.link.ranks > 0) {
           for (int q = 0; q < a.link.me; ++q) st_volatile_u32(a.link.src_acks[q] + xl::ack_index(a.link.me, 0), step_x);
           st_volatile_u32(a.link.counters, step_x);
         }
@@ -922,7 +972,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
 // the incoming rank state) and walks; the outgoing rank state is the state after the first tile of the
 // sequence.
 // ---------------------------------------------------------------------------
-template <int D, int E, bool FUSED>
+template <int D, int E, bool FUSED, bool PRE, bool LINK>
 __global__ void __launch_bounds__(320, 1) k_walk_dkv(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -937,6 +987,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
   uint8_t* sdn = smem + 6 * kBuf;
   __shared__ uint64_t kv_full[2], staged[2];
   __shared__ uint64_t qdo_full, dn_ready, a_done, ms_ready, sm_ready, b_done, l_done, e_free, l_free;
+  __shared__ uint64_t mapped;   // with a feature map: the workers have mapped the tile's Q and K in place
   __shared__ uint64_t ring_full[2], ring_scaled[2], ring_empty[2], sum_done;   // the span-total phase
   __shared__ uint32_t tmem_slot, step_s, step_x;
   __shared__ int dead;
@@ -952,6 +1003,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
       mbar_init(&ring_empty[p], 1);
     }
     mbar_init(&qdo_full, 1);
+    mbar_init(&mapped, kWorkers);
     mbar_init(&dn_ready, kWorkers);
     mbar_init(&a_done, 1);
     mbar_init(&ms_ready, kWorkers);
@@ -970,7 +1022,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
     prefetch_tensormap(&map_dv);
     if constexpr (FUSED) {
       step_s = a.coop ? ld_volatile_u32(a.sync) + 1 : 0;                       // this launch among those on the workspace
-      step_x = a.link.ranks > 0 ? ld_volatile_u32(a.link.counters) + 1 : 0;    // this hand-over in the group
+      step_x = LINK && a.link.ranks > 0 ? ld_volatile_u32(a.link.counters) + 1 : 0;    // this hand-over in the group
     }
   }
   if (warp == 2) tmem_alloc(&tmem_slot, 512);
@@ -1068,6 +1120,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
         // phase A.  The state tile as [N = d rows] x [K = e columns] (V Dn^T) and as [K = d rows] x
         // [N = e columns] (K Dn); T_dK, T_dV were drained by the previous epilogue, T_S by the state update
         wait_or_fault(&kv_full[p], ph, &dead, fault, kFaultTmaWait);
+        if (PRE && a.elu) wait_or_fault(&mapped, one, &dead, fault, kFaultMmaWait);
         wait_or_fault(&dn_ready, one, &dead, fault, kFaultMmaWait);
         if (i >= 1) {
           wait_or_fault(&e_free, one ^ 1, &dead, fault, kFaultMmaWait);
@@ -1102,12 +1155,21 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
     constexpr int kHalfE = E / 2;
     float Dn[kHalfE];  // this thread's part of the suffix state: row `row`, columns [half * E/2, (half+1) * E/2)
     float sl2 = 0.f, lam = 1.f;
+    // q and k enter as c * map(q), c * map(k): the map is applied to the tiles in shared memory, c is folded
+    // into factors that exist anyway
+    // (PRE = false: instantiations without any of this, for callers who bring q and k as they are)
+    const float c = PRE ? a.qk_scale : 1.f;
+    const bool elu = PRE && a.elu != 0;
     if (sums) {
       sl2 = a.s[my_bh % a.h] * kLog2e;
       for (int t = sum_t0, g = 0; t < sum_t1; ++t, ++g) {
         const int j = g & 1;
         wait_or_fault(&ring_full[j], (g >> 1) & 1, &dead, fault, kFaultTmaWait);
-        scale_row_pieces<D / 16>(sk[j], row, half * (D / 16), decay_pow(sl2, (t - sum_t0) * C + row), lane);
+        const float wt = c * decay_pow(sl2, (t - sum_t0) * C + row);
+        if (elu)
+          scale_row_pieces<D / 16, true>(sk[j], row, half * (D / 16), wt, lane);
+        else
+          scale_row_pieces<D / 16>(sk[j], row, half * (D / 16), wt, lane);
         fence_async_smem();
         mbar_arrive(&ring_scaled[j]);
       }
@@ -1170,7 +1232,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
               fma_state<kHalfE, D>(a.totals + (size_t)(w.bh * a.nspans + j) * D * E, row, half * kHalfE,
                                    decay_pow(sl2, (w.span_t0(j) - w.t1) * C), Dn);
           }
-          if (a.link.ranks > 0) {
+          if (LINK && a.link.ranks > 0) {
             // hand-over of the rank state inside the launch.  Dn holds the local part of the border state.
             const float sn = a.s[w.bh % a.h] * (float)a.n;
             const long long elems = (long long)(a.items / a.nspans) * D * E;
@@ -1230,13 +1292,21 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
         mbar_arrive(&dn_ready);
       }
       if (tid == 64) TRACE(1 + i * 6 + 0);
+      if (elu) {   // Q and K of this tile through the feature map before any product reads them
+        wait_or_fault(&kv_full[p], (i >> 1) & 1, &dead, fault, kFaultTmaWait);
+        wait_or_fault(&qdo_full, one, &dead, fault, kFaultTmaWait);
+        scale_row_pieces<D / 16, true>(sk[p], row, half * (D / 16), 1.f, lane);
+        scale_row_pieces<D / 16, true>(sq, row, half * (D / 16), 1.f, lane);
+        fence_async_smem();
+        mbar_arrive(&mapped);
+      }
       wait_or_fault(&a_done, one, &dead, fault, kFaultMmaWait);
       wait_or_fault(&qdo_full, one, &dead, fault, kFaultTmaWait);  // completed long ago: makes Q's bytes visible here
       if (tid == 64) TRACE(1 + i * 6 + 1);
       tc_fence_after_sync();
       // row-scaled copy of Q over the state operand (phase A has read it), then S_m over the K tile
       {
-        const float qd = decay_pow(sl2, row);
+        const float qd = c * decay_pow(sl2, row);
         constexpr int kPieces = D / 16;
         uint4 v[kPieces];
 #pragma unroll
@@ -1259,7 +1329,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int col0 = half * 64 + cc * 32;
-        masked_store32(t_s + lane_base + col0, sk[p], row, col0, sl2, lam);    // S_m over the K tile
+        masked_store32(t_s + lane_base + col0, sk[p], row, col0, sl2, lam, c * c);    // S_m over the K tile
       }
       fence_async_smem();
       tc_fence_before_sync();
@@ -1269,12 +1339,12 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int col0 = half * 64 + cc * 32;
-        masked_store32(t_ds + lane_base + col0, sv[p], row, col0, sl2, lam);   // dS_m over the V tile
+        masked_store32(t_ds + lane_base + col0, sv[p], row, col0, sl2, lam, c);   // dS_m (times Q's c) over the V tile
       }
 #pragma unroll
       for (int cc = 0; cc < D / 64; ++cc) scale_tmem32(t_dk + lane_base + half * (D / 2) + cc * 32, kd);
 #pragma unroll
-      for (int cc = 0; cc < E / 64; ++cc) scale_tmem32(t_dv + lane_base + half * (E / 2) + cc * 32, kd);
+      for (int cc = 0; cc < E / 64; ++cc) scale_tmem32(t_dv + lane_base + half * (E / 2) + cc * 32, kd * c);
       tmem_st_wait();
       fence_async_smem();
       tc_fence_before_sync();
@@ -1312,10 +1382,22 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
       // epilogue: dK and dV staged over S_m and dS_m (both read by phase B)
       wait_or_fault(&b_done, one, &dead, fault, kFaultMmaWait);
       tc_fence_after_sync();
+      if (elu || c != 1.f) {
+        // dk = dk' * c * map'(k), k read from the raw tensor (rows past the end of the sequence are not stored)
+        const bool live = row < len;
+        const __nv_bfloat16* raw =
+            static_cast<const __nv_bfloat16*>(a.raw) + ((size_t)w.bh * a.n + (size_t)w.t * C + (live ? row : 0)) * D;
 #pragma unroll
-      for (int cc = 0; cc < D / 64; ++cc) {
-        const int col0 = half * (D / 2) + cc * 32;
-        stage_row32(t_dk + lane_base + col0, kNoAcc, 0.f, sk[p], row, col0);
+        for (int cc = 0; cc < D / 64; ++cc) {
+          const int col0 = half * (D / 2) + cc * 32;
+          stage_row32_chain(t_dk + lane_base + col0, sk[p], row, col0, raw, c, elu && live);
+        }
+      } else {
+#pragma unroll
+        for (int cc = 0; cc < D / 64; ++cc) {
+          const int col0 = half * (D / 2) + cc * 32;
+          stage_row32(t_dk + lane_base + col0, kNoAcc, 0.f, sk[p], row, col0);
+        }
       }
 #pragma unroll
       for (int cc = 0; cc < E / 64; ++cc) {
@@ -1341,7 +1423,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
         st_volatile_u32(a.sync + 1, 0u);
         __threadfence();
         st_volatile_u32(a.sync, step_s);
-        if (a.link.ranks > 0) {
+        if (LINK && a.link.ranks > 0) {
           for (int q = 0; q < a.link.me; ++q) st_volatile_u32(a.link.src_acks[q] + xl::ack_index(a.link.me, 0), step_x);
           st_volatile_u32(a.link.counters, step_x);
         }
@@ -1414,8 +1496,8 @@ cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, size_t smem, cudaS
 
 constexpr long long kFlagWaitClocks = 1000000000LL;   // about half a second
 
-template <int D, int E, bool DQ, bool FUSED>
-cudaError_t launch_walk_out(const Dims& m, const void* x, const void* y, const void* z, void* out, WalkArgs a,
+template <int D, int E, bool DQ, bool FUSED, bool PRE, bool LINK>
+cudaError_t launch_walk_out_pre(const Dims& m, const void* x, const void* y, const void* z, void* out, WalkArgs a,
                             cudaStream_t st) {
   constexpr int WX = DQ ? E : D, WZ = DQ ? D : E;
   CUtensorMap mx, my, mz, mo;
@@ -1426,9 +1508,10 @@ cudaError_t launch_walk_out(const Dims& m, const void* x, const void* y, const v
   if ((err = seq_map(&mo, out, m, WZ, DQ ? "dq" : "o")) != cudaSuccess) return err;
   if ((err = fault_word_address(&a.fault)) != cudaSuccess) return err;
   const size_t smem = (size_t)7 * kBuf + 1024;
-  if ((err = opt_in_smem(k_walk_out<D, E, DQ, FUSED>, smem)) != cudaSuccess) return err;
+  if ((err = opt_in_smem(k_walk_out<D, E, DQ, FUSED, PRE, LINK>, smem)) != cudaSuccess) return err;
   a.h = m.h, a.n = m.n, a.tiles = m.tiles, a.span = m.span, a.nspans = m.nc, a.items = m.b * m.h * m.nc;
   a.wait_clocks = kFlagWaitClocks;
+  a.qk_scale = m.qk_scale, a.elu = m.qk_map;
   const bool waits = FUSED && (m.nc > 1 || a.link.ranks > 0);   // CTAs wait for one another: one span each, all resident
   a.coop = waits ? 1 : 0;
   if (waits) a.even = 1;
@@ -1437,7 +1520,7 @@ cudaError_t launch_walk_out(const Dims& m, const void* x, const void* y, const v
     g_failed_step = "fused walk kernel: more spans than SMs";
     return cudaErrorInvalidConfiguration;
   }
-  if ((err = launch_kernel(k_walk_out<D, E, DQ, FUSED>, grid_for(a.items), smem, st, mx, my, mz, mo, a)) !=
+  if ((err = launch_kernel(k_walk_out<D, E, DQ, FUSED, PRE, LINK>, grid_for(a.items), smem, st, mx, my, mz, mo, a)) !=
       cudaSuccess) {
     g_failed_step = "launch of a walk kernel";
     return err;
@@ -1445,8 +1528,8 @@ cudaError_t launch_walk_out(const Dims& m, const void* x, const void* y, const v
   return launched(DQ ? "launch of the dq walk kernel" : "launch of the forward walk kernel");
 }
 
-template <int D, int E, bool FUSED>
-cudaError_t launch_walk_dkv(const Dims& m, const void* q, const void* k, const void* v, const void* d_o, void* dk,
+template <int D, int E, bool FUSED, bool PRE, bool LINK>
+cudaError_t launch_walk_dkv_pre(const Dims& m, const void* q, const void* k, const void* v, const void* d_o, void* dk,
                             void* dv, WalkArgs a, cudaStream_t st) {
   CUtensorMap mq, mk, mv, mdo, mdk, mdv;
   cudaError_t err;
@@ -1457,10 +1540,12 @@ cudaError_t launch_walk_dkv(const Dims& m, const void* q, const void* k, const v
   if ((err = seq_map(&mdk, dk, m, D, "dk")) != cudaSuccess) return err;
   if ((err = seq_map(&mdv, dv, m, E, "dv")) != cudaSuccess) return err;
   if ((err = fault_word_address(&a.fault)) != cudaSuccess) return err;
+  a.raw = k;   // for the chain rule of a folded k preprocessing
   const size_t smem = (size_t)7 * kBuf + 1024;
-  if ((err = opt_in_smem(k_walk_dkv<D, E, FUSED>, smem)) != cudaSuccess) return err;
+  if ((err = opt_in_smem(k_walk_dkv<D, E, FUSED, PRE, LINK>, smem)) != cudaSuccess) return err;
   a.h = m.h, a.n = m.n, a.tiles = m.tiles, a.span = m.span, a.nspans = m.nc, a.items = m.b * m.h * m.nc;
   a.wait_clocks = kFlagWaitClocks;
+  a.qk_scale = m.qk_scale, a.elu = m.qk_map;
   const bool waits = FUSED && (m.nc > 1 || a.link.ranks > 0);
   a.coop = waits ? 1 : 0;
   if (waits) a.even = 1;
@@ -1469,12 +1554,51 @@ cudaError_t launch_walk_dkv(const Dims& m, const void* q, const void* k, const v
     g_failed_step = "fused walk kernel: more spans than SMs";
     return cudaErrorInvalidConfiguration;
   }
-  if ((err = launch_kernel(k_walk_dkv<D, E, FUSED>, grid_for(a.items), smem, st, mq, mk, mv, mdo, mdk, mdv, a)) !=
+  if ((err = launch_kernel(k_walk_dkv<D, E, FUSED, PRE, LINK>, grid_for(a.items), smem, st, mq, mk, mv, mdo, mdk, mdv, a)) !=
       cudaSuccess) {
     g_failed_step = "launch of the dk/dv walk kernel";
     return err;
   }
   return launched("launch of the dk/dv walk kernel");
+}
+
+// the instantiations with the q,k preprocessing only where it is asked for: the others keep the short code
+template <int D, int E, bool DQ, bool FUSED>
+cudaError_t launch_walk_out(const Dims& m, const void* x, const void* y, const void* z, void* out, WalkArgs a,
+                            cudaStream_t st) {
+  // ... and the hand-over code only in the launches of a sequence-parallel rank
+  const bool linked = a.link.ranks > 0;
+  if (has_qk_preprocessing(m)) {
+    if constexpr (FUSED) {
+      return linked ? launch_walk_out_pre<D, E, DQ, true, true, true>(m, x, y, z, out, a, st)
+                    : launch_walk_out_pre<D, E, DQ, true, true, false>(m, x, y, z, out, a, st);
+    } else if constexpr (DQ) {
+      return launch_walk_out_pre<D, E, true, false, true, false>(m, x, y, z, out, a, st);
+    }
+    g_failed_step = "q,k preprocessing is not part of the phase-by-phase schedule";
+    return cudaErrorInvalidValue;
+  }
+  if constexpr (FUSED) {
+    if (linked) return launch_walk_out_pre<D, E, DQ, true, false, true>(m, x, y, z, out, a, st);
+  }
+  return launch_walk_out_pre<D, E, DQ, FUSED, false, false>(m, x, y, z, out, a, st);
+}
+template <int D, int E, bool FUSED>
+cudaError_t launch_walk_dkv(const Dims& m, const void* q, const void* k, const void* v, const void* d_o, void* dk,
+                            void* dv, WalkArgs a, cudaStream_t st) {
+  const bool linked = a.link.ranks > 0;
+  if (has_qk_preprocessing(m)) {
+    if constexpr (FUSED) {
+      return linked ? launch_walk_dkv_pre<D, E, true, true, true>(m, q, k, v, d_o, dk, dv, a, st)
+                    : launch_walk_dkv_pre<D, E, true, true, false>(m, q, k, v, d_o, dk, dv, a, st);
+    }
+    g_failed_step = "q,k preprocessing is not part of the phase-by-phase schedule";
+    return cudaErrorInvalidValue;
+  }
+  if constexpr (FUSED) {
+    if (linked) return launch_walk_dkv_pre<D, E, true, false, true>(m, q, k, v, d_o, dk, dv, a, st);
+  }
+  return launch_walk_dkv_pre<D, E, FUSED, false, false>(m, q, k, v, d_o, dk, dv, a, st);
 }
 
 }  // namespace
@@ -1532,10 +1656,11 @@ cudaError_t walk_fwd_fused(const Dims& m, const void* q, const void* k, const vo
 #undef LASP_CALL
 }
 
-cudaError_t walk_bwd_dq(const Dims& m, const void* k, const void* v, const void* d_o, const float* s,
+cudaError_t walk_bwd_dq(const Dims& m, const void* q, const void* k, const void* v, const void* d_o, const float* s,
                         const float* prefix, const uint32_t* fwd_sync, void* dq, cudaStream_t st) {
   WalkArgs a = {};
   a.s = s, a.p0 = prefix, a.even_word = fwd_sync + kSyncEven;   // cut the sequences as the forward pass did
+  a.raw = q;                                                    // for the chain rule of a folded q preprocessing
 #define LASP_CALL(DD, EE) launch_walk_out<DD, EE, true, false>(m, d_o, v, k, dq, a, st)
   LASP_DISPATCH_DE(m, LASP_CALL);
 #undef LASP_CALL

@@ -17,6 +17,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _cabi
+from ._cabi import LaspLibraryError, LaspStatusError  # noqa: F401  (what the calls below raise)
 
 _DTYPES = {torch.float32: _cabi.F32, torch.bfloat16: _cabi.BF16, torch.float16: _cabi.F16}
 _PATHS = {"auto": _cabi.PATH_AUTO, "simt": _cabi.PATH_SIMT, "tensor": _cabi.PATH_TENSOR}
@@ -96,13 +97,19 @@ def _require_cuda(*ts):
                                f"got a tensor on {t.device}")
 
 
-def make_plan(b: int, h: int, n: int, d: int, e: int, dtype: torch.dtype, path: str | None = None) -> Plan:
+def make_plan(b: int, h: int, n: int, d: int, e: int, dtype: torch.dtype, path: str | None = None,
+              qk_scale: float = 1.0, feature_map: str | None = None) -> Plan:
+    """``qk_scale`` / ``feature_map`` ("elu1"): the operator is evaluated on qk_scale * map(q), qk_scale * map(k)
+    inside the kernels (lasp_problem.qk_map, .qk_scale); raises LaspStatusError when the problem's kernels
+    cannot do that."""
     if dtype not in _DTYPES:
         raise TypeError(f"unsupported dtype {dtype}; use float32, bfloat16 or float16")
     name = path or default_path()
     if name not in _PATHS:
         raise ValueError(f"unknown kernel path {name!r}; use auto, simt or tensor")
-    prob = _cabi.Problem(b, h, n, d, e, _DTYPES[dtype], _PATHS[name], 0)
+    if feature_map not in _cabi.QK_MAPS:
+        raise ValueError(f"unknown feature map {feature_map!r}; use None or 'elu1'")
+    prob = _cabi.Problem(b, h, n, d, e, _DTYPES[dtype], _PATHS[name], _cabi.QK_MAPS[feature_map], float(qk_scale))
     resolved = _cabi.call("lasp_b200_resolve_path", C.byref(prob))
     prob.path = resolved
     chunk = _cabi.call("lasp_b200_chunk_tokens", C.byref(prob))

@@ -17,11 +17,13 @@ from . import comm, engine
 
 
 class FixedStep:
-    def __init__(self, q, k, v, do, s, group=None):
+    def __init__(self, q, k, v, do, s, group=None, qk_scale=1.0, feature_map=None):
+        """``qk_scale`` / ``feature_map``: the operator on qk_scale * map(q), qk_scale * map(k), folded into the
+        kernels (engine.make_plan)."""
         b, h, n, d = q.shape
         e = v.shape[-1]
         self.n, self.s = n, s
-        self.plan = engine.make_plan(b, h, n, d, e, q.dtype)
+        self.plan = engine.make_plan(b, h, n, d, e, q.dtype, qk_scale=qk_scale, feature_map=feature_map)
         self.relay = None
         self.rank, self.last = 0, 0
         if group is not None and torch.distributed.get_world_size(group) > 1:

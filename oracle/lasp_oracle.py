@@ -232,6 +232,34 @@ def fwd_bwd(q, k, v, s, do, block: int = BLOCK, dtype=torch.float32):
 # ----------------------------------------------------------------------------
 # sequence-parallel chain, emulated in one process
 # ----------------------------------------------------------------------------
+def preprocess_qk(x, qk_scale: float = 1.0, feature_map: Optional[str] = None):
+    """qk_scale * map(x): what a caller of the reference applies to q and k in front of the operator
+    (elu(x)+1 in the no-decay configuration, d^-0.5 elsewhere); lasp/lightning_attention.py:510 takes the result."""
+    if feature_map == "elu1":
+        x = torch.nn.functional.elu(x) + 1.0
+    elif feature_map is not None:
+        raise ValueError(feature_map)
+    return x * qk_scale
+
+
+def preprocess_slope(x, qk_scale: float = 1.0, feature_map: Optional[str] = None):
+    """d(preprocess_qk(x))/dx, elementwise."""
+    if feature_map == "elu1":
+        return qk_scale * torch.where(x > 0, torch.ones_like(x), torch.exp(x))
+    return torch.full_like(x, qk_scale)
+
+
+def fwd_bwd_preprocessed(q, k, v, s, do, qk_scale: float = 1.0, feature_map: Optional[str] = None,
+                         block: int = BLOCK, dtype=torch.float32):
+    """o, dq, dk, dv of the operator evaluated on preprocess_qk(q), preprocess_qk(k), the gradients taken with
+    respect to the RAW q and k (chain rule written out): what the kernels with the preprocessing folded into
+    their load path must return."""
+    qd, kd = q.to(dtype), k.to(dtype)
+    o, dqm, dkm, dv = fwd_bwd(preprocess_qk(qd, qk_scale, feature_map), preprocess_qk(kd, qk_scale, feature_map), v, s, do,
+                              block=block, dtype=dtype)
+    return (o, dqm * preprocess_slope(qd, qk_scale, feature_map), dkm * preprocess_slope(kd, qk_scale, feature_map), dv)
+
+
 def sp_chain(q, k, v, s, do, sp: int, block: int = BLOCK, dtype=torch.float32):
     """Rank recurrence of lasp/lasp_naive.py:547-568 (forward, rank r -> r+1)
     and :593-616 (backward, rank r -> r-1) over ``sp`` contiguous chunks.

@@ -42,7 +42,7 @@ def test_abi_version_and_strerror(lib):
 
 
 def _problem(**kw):
-    base = dict(b=2, h=3, n=256, d=64, e=64, dtype=_cabi.F32, path=_cabi.PATH_AUTO, reserved=0)
+    base = dict(b=2, h=3, n=256, d=64, e=64, dtype=_cabi.F32, path=_cabi.PATH_AUTO, qk_map=0, qk_scale=0.0)
     base.update(kw)
     return _cabi.Problem(**base)
 

@@ -411,6 +411,84 @@ def test_no_decay_linear_transformer_config_bf16(width):
         assert O.max_rel_err(t, w) < gate, (key, width)
 
 
+def run_lightning_fused(q, k, v, do, s, dtype, qk_scale, feature_map):
+    from lasp_b200 import lightning_attn_fused
+    qd, kd, vd, dod = (t.to(DEV, dtype) for t in (q, k, v, do))
+    qd.requires_grad_(True), kd.requires_grad_(True), vd.requires_grad_(True)
+    o = lightning_attn_fused(qd, kd, vd, s.to(DEV), qk_scale=qk_scale, feature_map=feature_map)
+    o.backward(dod)
+    torch.cuda.synchronize()
+    return o.detach(), qd.grad, kd.grad, vd.grad
+
+
+def test_folded_preprocessing_reproduces_the_reference_elu_case():
+    """elu(x)+1 folded into the kernels, on the RAW draws of the reference's no-decay case (bf16, tensor-core
+    kernels): the output must be the reference's output for the mapped inputs, dv its dv, and dq, dk its
+    gradients times the slope of the map."""
+    from lasp_b200 import _core
+    p = dict(CASES["single"]["lightning_fp32_nodecay_elu"])
+    g = load_golden("lightning_fp32_nodecay_elu")
+    q, k, v, do, s = case_inputs(dict(p, feature_map=None))
+    qb, kb = q.to(torch.bfloat16), k.to(torch.bfloat16)
+    assert _core.kernels_preprocess(qb.to(DEV), v.to(DEV, torch.bfloat16), 1.0, "elu1")   # really in the kernels
+    o, dq, dk, dv = run_lightning_fused(q, k, v, do, s, torch.bfloat16, 1.0, "elu1")
+    assert O.max_rel_err(o, golden_tensor(g["o"])) < TOL_BF16
+    assert O.max_rel_err(dv, golden_tensor(g["dv"])) < TOL_BF16
+    assert O.max_rel_err(dq, golden_tensor(g["dq"]) * O.preprocess_slope(qb.float(), 1.0, "elu1")) < TOL_BF16
+    assert O.max_rel_err(dk, golden_tensor(g["dk"]) * O.preprocess_slope(kb.float(), 1.0, "elu1")) < TOL_BF16
+
+
+FOLDED = [  # b, h, n, d, e, slopes, scale, map
+    (2, 3, 512, 128, 128, "baseline", 128 ** -0.5, None),
+    (2, 3, 512, 128, 128, "zero", 1.0, "elu1"),
+    (1, 2, 333, 64, 128, "baseline", 0.5, "elu1"),
+    (1, 4, 1100, 128, 64, "zero", 64 ** -0.5, "elu1"),
+    (2, 12, 2048, 128, 128, "baseline", 128 ** -0.5, "elu1"),     # several spans per sequence: the fused launches
+    (4, 40, 256, 64, 64, "steep", 0.25, "elu1"),                  # more sequences than SMs
+    (1, 2, 384, 256, 256, "zero", 1.0, "elu1"),                   # 128-wide slices stacked along the batch
+]
+
+
+@pytest.mark.parametrize("b,h,n,d,e,slopes,scale,fmap", FOLDED)
+def test_folded_preprocessing_matches_oracle(b, h, n, d, e, slopes, scale, fmap):
+    """qk_scale * map(.) of q and k inside the tensor-core kernels, gradients with respect to the raw q, k,
+    against the oracle with the chain rule written out (ragged n, both head widths, with and without decay)."""
+    from lasp_b200 import _core
+    q, k, v, do = O.make_inputs(500 + n + d, b, h, n, d, e, scale_qk=False)
+    s = {"baseline": O.baseline_slopes(h), "zero": torch.zeros(h, 1, 1),
+         "steep": torch.full((h, 1, 1), 0.6)}[slopes]
+    r = [t.to(torch.bfloat16).float() for t in (q, k, v, do)]
+    assert _core.kernels_preprocess(q[..., :128].to(DEV, torch.bfloat16), v[..., :128].to(DEV, torch.bfloat16), scale, fmap)
+    got = run_lightning_fused(q, k, v, do, s, torch.bfloat16, scale, fmap)
+    if d <= 128:
+        ref = O.fwd_bwd_preprocessed(r[0], r[1], r[2], s, r[3], scale, fmap)
+    else:
+        o, dqm, dkm, dv = O.dense_closed_form(O.preprocess_qk(r[0], scale, fmap), O.preprocess_qk(r[1], scale, fmap),
+                                              r[2], s, r[3])
+        ref = (o, dqm * O.preprocess_slope(r[0], scale, fmap), dkm * O.preprocess_slope(r[1], scale, fmap), dv)
+    gate = TOL_BF16 if d <= 128 else 2.5e-2
+    for t, w, key in zip(got, ref, ("o", "dq", "dk", "dv")):
+        assert O.max_rel_err(t, w) < gate, key
+    # and the same numbers as the preprocessing done by the caller in front of the plain operator
+    qm = O.preprocess_qk(r[0], scale, fmap).to(torch.bfloat16).float()
+    km = O.preprocess_qk(r[1], scale, fmap).to(torch.bfloat16).float()
+    plain = run_lightning(qm, km, r[2], r[3], s, torch.bfloat16)
+    assert O.max_rel_err(got[0], plain[0].float()) < TOL_BF16
+    assert O.max_rel_err(got[3], plain[3].float()) < TOL_BF16
+
+
+def test_folded_preprocessing_falls_back_to_torch_where_the_kernels_cannot():
+    """fp32 inputs run on the FFMA kernels, which have no folded preprocessing: same result through torch."""
+    from lasp_b200 import _core
+    q, k, v, do = O.make_inputs(77, 1, 2, 200, 64, 64, scale_qk=False)
+    s = O.baseline_slopes(2)
+    assert not _core.kernels_preprocess(q.to(DEV), v.to(DEV), 0.125, "elu1")
+    got = run_lightning_fused(q, k, v, do, s, torch.float32, 0.125, "elu1")
+    ref = O.fwd_bwd_preprocessed(q, k, v, s, do, 0.125, "elu1")
+    for t, w, key in zip(got, ref, ("o", "dq", "dk", "dv")):
+        assert O.max_rel_err(t, w) < TOL_FP32, key
+
+
 def test_exchange_wait_runs_out_and_is_reported():
     """Failure detection without a GPU fault: the last rank of a group of two whose sender never writes.  The
     hand-over kernel's waits are bounded, so it must come back on its own, set the relay bit (4) of the fault

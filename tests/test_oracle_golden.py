@@ -95,6 +95,28 @@ def test_incoming_states_equal_longer_sequence():
         assert O.max_rel_err(torch.cat([g[i] for g in grads], 2), ref[i + 1]) < 1e-12
 
 
+def test_preprocessed_oracle_against_the_reference_and_autograd():
+    """The operator with q,k preprocessing folded in: on the raw inputs of the reference's no-decay elu(x)+1 case
+    it must reproduce the reference's output, its dk, dq times the map's slope, and what autograd gives."""
+    p = dict(CASES["single"]["lightning_fp32_nodecay_elu"])
+    g = load_golden("lightning_fp32_nodecay_elu")
+    raw = dict(p, feature_map=None)
+    q, k, v, do, s = case_inputs(raw)                      # the same draws, before elu(x)+1
+    o, dq, dk, dv = O.fwd_bwd_preprocessed(q, k, v, s, do, 1.0, "elu1")
+    assert O.max_rel_err(o, golden_tensor(g["o"])) < TOL
+    assert O.max_rel_err(dv, golden_tensor(g["dv"])) < TOL
+    assert O.max_rel_err(dq, golden_tensor(g["dq"]) * O.preprocess_slope(q, 1.0, "elu1")) < TOL
+    assert O.max_rel_err(dk, golden_tensor(g["dk"]) * O.preprocess_slope(k, 1.0, "elu1")) < TOL
+    # and with a scale, against autograd through the dense closed form in fp64
+    c = 0.37
+    qd, kd, vd = (t.double().requires_grad_(True) for t in (q, k, v))
+    od = O.dense_closed_form(O.preprocess_qk(qd, c, "elu1"), O.preprocess_qk(kd, c, "elu1"), vd, s)
+    od.backward(do.double())
+    got = O.fwd_bwd_preprocessed(q, k, v, s, do, c, "elu1", dtype=torch.float64)
+    for t, r in zip(got, (od.detach(), qd.grad, kd.grad, vd.grad)):
+        assert O.max_rel_err(t, r) < 1e-10
+
+
 def test_slopes_match_reference_function(golden_dir):
     with np.load(golden_dir + "/build_slope_tensor.npz") as z:
         for key in z.files:
