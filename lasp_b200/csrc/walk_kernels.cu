@@ -746,7 +746,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       mbar_arrive(&ys_ready);
       if (tid == 64) TRACE(1 + i * 6 + 2);
       // masked scores, packed to bf16 in place: they are the A operand of O1 straight from tensor memory
-#pragma unroll
+#pragma unroll 1
       for (int cc = 0; cc < 2; ++cc) {
         uint32_t packed[16];
         masked_pack32<false>(t_s[p] + lane_base + half * 64 + cc * 32, row, half * 64 + cc * 32, sl2, lam, packed, c_mask);
@@ -757,7 +757,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       mbar_arrive(&sm_ready[p]);
       if (tid == 64) TRACE(1 + i * 6 + 3);
       if (elu && i + 1 < total) map_tile(i + 1);   // the next tile's S can then go out under this tile's work
-      if (w.first_of_item()) {
+      if (__builtin_expect(w.first_of_item(), 0)) {   // once per span: kept out of the tiles' straight-line code
         // the state at the span border (the score work above does not need it, so the wait for the other
         // CTAs' totals hides behind it); the O2 MMA that read the operand tile of the previous item has completed
         if constexpr (!FUSED) {
@@ -859,7 +859,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
       tc_fence_after_sync();
       {
         const float qd = c_o2 * decay_pow(sl2, row);
-#pragma unroll
+#pragma unroll 1
         for (int cc = 0; cc < WZ / 64; ++cc) scale_tmem32(t_o + lane_base + half * (WZ / 2) + cc * 32, qd);
       }
       tmem_st_wait();
@@ -902,13 +902,13 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
         const bool live = row < len;
         const __nv_bfloat16* raw =
             static_cast<const __nv_bfloat16*>(a.raw) + ((size_t)w.bh * a.n + (size_t)w.t * C + (live ? row : 0)) * WZ;
-#pragma unroll
+#pragma unroll 1
         for (int cc = 0; cc < WZ / 64; ++cc) {
           const int col0 = half * (WZ / 2) + cc * 32;
           stage_row32_chain(t_o + lane_base + col0, sy[p], row, col0, raw, c, elu && live);
         }
       } else {
-#pragma unroll
+#pragma unroll 1
         for (int cc = 0; cc < WZ / 64; ++cc) {
           const int col0 = half * (WZ / 2) + cc * 32;
           stage_row32(t_o + lane_base + col0, kNoAcc, 0.f, sy[p], row, col0);
@@ -1197,7 +1197,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
     for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++i) {
       const int p = i & 1, one = i & 1;
       const int len = min(C, a.n - w.t * C);
-      if (w.first_of_item()) {
+      if (__builtin_expect(w.first_of_item(), 0)) {   // once per span: kept out of the tiles' straight-line code
         sl2 = a.s[w.bh % a.h] * kLog2e;
         lam = exp2f(-sl2);
         if constexpr (!FUSED) {
@@ -1326,7 +1326,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
           *reinterpret_cast<uint4*>(sdn + (piece >> 3) * C * 128 + row * 128 + (piece & 7) * 16) = v[q];
         }
       }
-#pragma unroll
+#pragma unroll 1
       for (int cc = 0; cc < 2; ++cc) {
         const int col0 = half * 64 + cc * 32;
         masked_store32(t_s + lane_base + col0, sk[p], row, col0, sl2, lam, c * c);    // S_m over the K tile
@@ -1336,14 +1336,14 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
       mbar_arrive(&ms_ready);
       if (tid == 64) TRACE(1 + i * 6 + 2);
       const float kd = decay_pow(sl2, max(len - row, 0));
-#pragma unroll
+#pragma unroll 1
       for (int cc = 0; cc < 2; ++cc) {
         const int col0 = half * 64 + cc * 32;
         masked_store32(t_ds + lane_base + col0, sv[p], row, col0, sl2, lam, c);   // dS_m (times Q's c) over the V tile
       }
-#pragma unroll
+#pragma unroll 1
       for (int cc = 0; cc < D / 64; ++cc) scale_tmem32(t_dk + lane_base + half * (D / 2) + cc * 32, kd);
-#pragma unroll
+#pragma unroll 1
       for (int cc = 0; cc < E / 64; ++cc) scale_tmem32(t_dv + lane_base + half * (E / 2) + cc * 32, kd * c);
       tmem_st_wait();
       fence_async_smem();
@@ -1387,19 +1387,19 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
         const bool live = row < len;
         const __nv_bfloat16* raw =
             static_cast<const __nv_bfloat16*>(a.raw) + ((size_t)w.bh * a.n + (size_t)w.t * C + (live ? row : 0)) * D;
-#pragma unroll
+#pragma unroll 1
         for (int cc = 0; cc < D / 64; ++cc) {
           const int col0 = half * (D / 2) + cc * 32;
           stage_row32_chain(t_dk + lane_base + col0, sk[p], row, col0, raw, c, elu && live);
         }
       } else {
-#pragma unroll
+#pragma unroll 1
         for (int cc = 0; cc < D / 64; ++cc) {
           const int col0 = half * (D / 2) + cc * 32;
           stage_row32(t_dk + lane_base + col0, kNoAcc, 0.f, sk[p], row, col0);
         }
       }
-#pragma unroll
+#pragma unroll 1
       for (int cc = 0; cc < E / 64; ++cc) {
         const int col0 = half * (E / 2) + cc * 32;
         stage_row32(t_dv + lane_base + col0, kNoAcc, 0.f, sv[p], row, col0);
