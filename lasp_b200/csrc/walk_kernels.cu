@@ -40,6 +40,24 @@ __device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u6
 #endif
 
 constexpr int kBuf = 32768;       // one shared-memory buffer: a 128 x 128 bf16 tile
+
+// Two buffers of a double-buffered tile / two accumulators, addressed by arithmetic: an array of two pointers
+// indexed by the tile's parity would live in local memory, and the tile loops look these up all the time.
+struct BufPair {
+  uint8_t* base;
+  __device__ __forceinline__ uint8_t* operator[](int p) const { return base + p * kBuf; }
+};
+struct TmemPair {
+  uint32_t base;
+  __device__ __forceinline__ uint32_t operator[](int p) const { return base + p * 128; }
+};
+struct IntPair {
+  int a, b;
+  __device__ __forceinline__ int get(int p) const { return p ? b : a; }
+  __device__ __forceinline__ void set(int p, int v) {
+    if (p) b = v; else a = v;
+  }
+};
 constexpr int kWorkers = 256;     // warps 2..9
 
 // Global-memory image of a d x e span state in lane order (see common.cuh): this thread's part is row
@@ -452,9 +470,9 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
   constexpr int WZ = DQ ? D : E;  // width of Z and OUT
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
-  uint8_t* sx[2] = {smem, smem + kBuf};
-  uint8_t* sy[2] = {smem + 2 * kBuf, smem + 3 * kBuf};
-  uint8_t* sz[2] = {smem + 4 * kBuf, smem + 5 * kBuf};
+  const BufPair sx{smem};
+  const BufPair sy{smem + 2 * kBuf};
+  const BufPair sz{smem + 4 * kBuf};
   uint8_t* sp = smem + 6 * kBuf;
   __shared__ uint64_t x_full[2], y_full[2], z_full[2], s_full[2], sm_ready[2], o_full[2], o2_full[2], staged[2];
   __shared__ uint64_t p_ready, l_free, o_free, ys_ready, o2s_ready, l_full;
@@ -505,7 +523,8 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
   const uint32_t tmem = tmem_slot;
   if (tid == 64) TRACE(0);
   if (tid == 64) GTRACE(57);
-  const uint32_t t_s[2] = {tmem, tmem + 128}, t_o = tmem + 256, t_l = tmem + 384;
+  const TmemPair t_s{tmem};
+  const uint32_t t_o = tmem + 256, t_l = tmem + 384;
   TileWalk w{a.items, a.nspans, a.span, a.tiles, 0, false, even_s != 0};
   // the span-total phase: only with several spans per sequence, and then this CTA has one span
   bool sums = false;
@@ -539,7 +558,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
         wait_or_fault(&sum_done, 0, &dead, fault, kFaultMmaWait);   // the MMAs have read every ring stage
       }
       int i = 0;
-      int out_row[2] = {0, 0}, out_bh[2] = {0, 0};
+      IntPair out_row{0, 0}, out_bh{0, 0};
       for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++i) {
         const int p = i & 1, u = i >> 1;
         if (i >= x_issued) {
@@ -553,19 +572,19 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
         if (i >= 2) {
           // the output of tile i-2 is staged in Y's buffer: store it, then reuse the buffer
           wait_or_fault(&staged[p], (u - 1) & 1, &dead, fault, kFaultMmaWait);
-          tma_store_4d(&map_out, sy[p], 0, out_row[p], 0, out_bh[p]);
+          tma_store_4d(&map_out, sy[p], 0, out_row.get(p), 0, out_bh.get(p));
           bulk_commit();
           bulk_wait_read<0>();
         }
         mbar_expect_tx(&y_full[p], C * WX * 2);
         tma_load_4d(sy[p], &map_y, &y_full[p], 0, w.t * C, 0, w.bh);
-        out_row[p] = w.t * C;
-        out_bh[p] = w.bh;
+        out_row.set(p, w.t * C);
+        out_bh.set(p, w.bh);
       }
       for (int j = (i >= 2 ? i - 2 : 0); j < i; ++j) {   // the last two tiles
         const int p = j & 1, u = j >> 1;
         wait_or_fault(&staged[p], u & 1, &dead, fault, kFaultMmaWait);
-        tma_store_4d(&map_out, sy[p], 0, out_row[p], 0, out_bh[p]);
+        tma_store_4d(&map_out, sy[p], 0, out_row.get(p), 0, out_bh.get(p));
         bulk_commit();
       }
       bulk_wait_all<0>();
@@ -982,8 +1001,8 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
   uint8_t* smem = align1024(smem_raw);
   uint8_t* sq = smem;
   uint8_t* sdo = smem + kBuf;
-  uint8_t* sk[2] = {smem + 2 * kBuf, smem + 3 * kBuf};
-  uint8_t* sv[2] = {smem + 4 * kBuf, smem + 5 * kBuf};
+  const BufPair sk{smem + 2 * kBuf};
+  const BufPair sv{smem + 4 * kBuf};
   uint8_t* sdn = smem + 6 * kBuf;
   __shared__ uint64_t kv_full[2], staged[2];
   __shared__ uint64_t qdo_full, dn_ready, a_done, ms_ready, sm_ready, b_done, l_done, e_free, l_free;
@@ -1067,14 +1086,14 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
         wait_or_fault(&sum_done, 0, &dead, fault, kFaultMmaWait);   // the MMAs have read every ring stage
       }
       int i = 0;
-      int out_row[2] = {0, 0}, out_bh[2] = {0, 0};
+      IntPair out_row{0, 0}, out_bh{0, 0};
       for (bool ok = w.start(blockIdx.x, gridDim.x); ok; ok = w.next(), ++i) {
         const int p = i & 1, u = i >> 1;
         if (i >= 2) {
           // dK and dV of tile i-2 are staged in this parity's K and V buffers
           wait_or_fault(&staged[p], (u - 1) & 1, &dead, fault, kFaultMmaWait);
-          tma_store_4d(&map_dk, sk[p], 0, out_row[p], 0, out_bh[p]);
-          tma_store_4d(&map_dv, sv[p], 0, out_row[p], 0, out_bh[p]);
+          tma_store_4d(&map_dk, sk[p], 0, out_row.get(p), 0, out_bh.get(p));
+          tma_store_4d(&map_dv, sv[p], 0, out_row.get(p), 0, out_bh.get(p));
           bulk_commit();
           bulk_wait_read<0>();
         }
@@ -1090,14 +1109,14 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
           tma_load_4d(sq, &map_q, &qdo_full, 0, w.t * C, 0, w.bh);
           tma_load_4d(sdo, &map_do, &qdo_full, 0, w.t * C, 0, w.bh);
         }
-        out_row[p] = w.t * C;
-        out_bh[p] = w.bh;
+        out_row.set(p, w.t * C);
+        out_bh.set(p, w.bh);
       }
       for (int j = (i >= 2 ? i - 2 : 0); j < i; ++j) {   // the last two tiles
         const int p = j & 1, u = j >> 1;
         wait_or_fault(&staged[p], u & 1, &dead, fault, kFaultMmaWait);
-        tma_store_4d(&map_dk, sk[p], 0, out_row[p], 0, out_bh[p]);
-        tma_store_4d(&map_dv, sv[p], 0, out_row[p], 0, out_bh[p]);
+        tma_store_4d(&map_dk, sk[p], 0, out_row.get(p), 0, out_bh.get(p));
+        tma_store_4d(&map_dv, sv[p], 0, out_row.get(p), 0, out_bh.get(p));
         bulk_commit();
       }
       bulk_wait_all<0>();
@@ -1326,25 +1345,28 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
           *reinterpret_cast<uint4*>(sdn + (piece >> 3) * C * 128 + row * 128 + (piece & 7) * 16) = v[q];
         }
       }
+      // S_m over the K tile, then dS_m (times Q's c) over the V tile: one piece of code for the four blocks (the
+      // tile loop runs the faster the less code it spans)
 #pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int col0 = half * 64 + cc * 32;
-        masked_store32(t_s + lane_base + col0, sk[p], row, col0, sl2, lam, c * c);    // S_m over the K tile
+      for (int u = 0; u < 4; ++u) {
+        const int col0 = half * 64 + (u & 1) * 32;
+        if (u == 2) {   // S_m is complete: the state update's product can go out
+          fence_async_smem();
+          tc_fence_before_sync();
+          mbar_arrive(&ms_ready);
+        }
+        masked_store32((u < 2 ? t_s : t_ds) + lane_base + col0, (u < 2 ? sk : sv)[p], row, col0, sl2, lam,
+                       u < 2 ? c * c : c);
       }
-      fence_async_smem();
-      tc_fence_before_sync();
-      mbar_arrive(&ms_ready);
       if (tid == 64) TRACE(1 + i * 6 + 2);
       const float kd = decay_pow(sl2, max(len - row, 0));
+      // the two state products take their row decay in place (32 columns at a time, dK's blocks then dV's)
 #pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int col0 = half * 64 + cc * 32;
-        masked_store32(t_ds + lane_base + col0, sv[p], row, col0, sl2, lam, c);   // dS_m (times Q's c) over the V tile
+      for (int u = 0; u < D / 64 + E / 64; ++u) {
+        const bool dv_part = u >= D / 64;
+        const int cc = dv_part ? u - D / 64 : u;
+        scale_tmem32((dv_part ? t_dv + half * (E / 2) : t_dk + half * (D / 2)) + lane_base + cc * 32, dv_part ? kd * c : kd);
       }
-#pragma unroll 1
-      for (int cc = 0; cc < D / 64; ++cc) scale_tmem32(t_dk + lane_base + half * (D / 2) + cc * 32, kd);
-#pragma unroll 1
-      for (int cc = 0; cc < E / 64; ++cc) scale_tmem32(t_dv + lane_base + half * (E / 2) + cc * 32, kd * c);
       tmem_st_wait();
       fence_async_smem();
       tc_fence_before_sync();
@@ -1392,17 +1414,15 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
           const int col0 = half * (D / 2) + cc * 32;
           stage_row32_chain(t_dk + lane_base + col0, sk[p], row, col0, raw, c, elu && live);
         }
-      } else {
-#pragma unroll 1
-        for (int cc = 0; cc < D / 64; ++cc) {
-          const int col0 = half * (D / 2) + cc * 32;
-          stage_row32(t_dk + lane_base + col0, kNoAcc, 0.f, sk[p], row, col0);
-        }
       }
+      // dV's blocks, and dK's too unless the chain rule above has staged them: one loop
 #pragma unroll 1
-      for (int cc = 0; cc < E / 64; ++cc) {
-        const int col0 = half * (E / 2) + cc * 32;
-        stage_row32(t_dv + lane_base + col0, kNoAcc, 0.f, sv[p], row, col0);
+      for (int u = (elu || c != 1.f) ? D / 64 : 0; u < D / 64 + E / 64; ++u) {
+        const bool dv_part = u >= D / 64;
+        const int cc = dv_part ? u - D / 64 : u;
+        const int col0 = half * ((dv_part ? E : D) / 2) + cc * 32;
+        stage_row32((dv_part ? t_dv : t_dk) + lane_base + col0, kNoAcc, 0.f, (dv_part ? sv : sk)[p], row,
+                    col0);
       }
       tc_fence_before_sync();
       mbar_arrive(&e_free);
