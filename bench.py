@@ -215,7 +215,7 @@ def run_reference(args, cfg):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def run_reference_triton(args, cfg):
@@ -261,7 +261,7 @@ def run_reference_triton(args, cfg):
         line.update(value=cfg["b"] * cfg["n"] / (ms * 1e-3), ms_per_step=ms, higher_is_better=True)
     except BaseException as exc:  # noqa: BLE001  (a Triton compile error must become the line, not a crash)
         line["unavailable"] = f"{type(exc).__name__}: {str(exc).splitlines()[0] if str(exc) else ''}"[:300]
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def metric_name(cfg):
@@ -308,8 +308,8 @@ def run_kernels_only(args, cfg):
     for i in range(args.warmup + args.steps):
         steps[i % n_sets].run()
     torch.cuda.synchronize()
-    print(json.dumps({"kernels_only": True, "steps": args.steps, "warmup": args.warmup, "launches_per_step":
-                      steps[0].launches, "config": args.config, "kernel_faults": engine.read_status()}), flush=True)
+    emit({"kernels_only": True, "steps": args.steps, "warmup": args.warmup, "launches_per_step":
+                      steps[0].launches, "config": args.config, "kernel_faults": engine.read_status()})
 
 
 def run_ours(args, cfg):
@@ -428,7 +428,7 @@ def run_ours(args, cfg):
                       paths=["graph of C-ABI launches", "lasp_fuse_parallel"] if graphs else ["lasp_fuse_parallel"])
         if max(worst.tolist()) > PARITY_GATE or any(x != x for x in worst.tolist()):
             if rank == 0:
-                print(json.dumps({"error": "parity gate exceeded", "parity": parity}), flush=True)
+                emit({"error": "parity gate exceeded", "parity": parity})
             raise SystemExit(3)
 
     def step(i):
@@ -646,13 +646,34 @@ def run_ours(args, cfg):
     if world == 1:
         cpu_value, cores, _, sample = cpu_port_tokens_per_s(cfg, 3)
         line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result():
+    """Libraries print to stdout too (NCCL its version, for one): everything but the result line goes to stderr."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    text = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(text.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, text)
+
+
 def main():
+    keep_stdout_for_the_result()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

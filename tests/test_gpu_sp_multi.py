@@ -85,6 +85,36 @@ def _worker(rank, world, port, mode, params, errq):
             rows = [i * p["dp"] + dp_rank for i in range(bl)]   # batch interleaved over dp
             qi, ki, vi, doi = (torch.stack([piece(w, bg, sp_rank) for bg in rows]).to(dtype).to(dev)
                                for w in range(4))
+        if mode == "fold":
+            # the operator with the q,k preprocessing folded into the kernels, on the raw draws; the oracle chain
+            # runs on the preprocessed tensors and its dq, dk take the chain rule afterwards
+            import lasp_b200
+            c, fmap = p["fold"]
+            bl_, h_, _, d_ = qi.shape
+            qi.requires_grad_(True), ki.requires_grad_(True), vi.requires_grad_(True)
+            KV = torch.full((bl_, h_, d_, p["e"]), float("nan"), device=dev)
+            DKV = torch.full((bl_, h_, d_, p["e"]), float("nan"), device=dev)
+            oi = lasp_b200.lasp_fuse_parallel_fused(qi, ki, vi, s.to(dev), KV, DKV, qk_scale=c, feature_map=fmap)
+            oi.backward(doi)
+            torch.cuda.synchronize()
+            lasp_b200.check_faults()
+            heads = p["check_heads"]
+            gq, gk, gv, gdo = (torch.stack([torch.cat([piece(w, bg, r)[heads] for r in range(p["sp"])], 1)
+                                            for bg in rows]).to(dtype).float() for w in range(4))
+            outs, grads, _ = O.sp_chain(O.preprocess_qk(gq, c, fmap), O.preprocess_qk(gk, c, fmap), gv, s[heads], gdo,
+                                        p["sp"])
+            mine = slice(sp_rank * nl, (sp_rank + 1) * nl)
+            ref = dict(o=outs[sp_rank], dq=grads[sp_rank][0] * O.preprocess_slope(gq[:, :, mine], c, fmap),
+                       dk=grads[sp_rank][1] * O.preprocess_slope(gk[:, :, mine], c, fmap), dv=grads[sp_rank][2])
+            res = dict(o=oi.detach().float().cpu(), dq=qi.grad.float().cpu(), dk=ki.grad.float().cpu(),
+                       dv=vi.grad.float().cpu())
+            for nm, t in res.items():
+                err = O.max_rel_err(t[:, heads], ref[nm])
+                assert err < TOL_BF16, ("fuse_parallel_fused", nm, rank, err)
+            assert engine.read_status() == 0
+            dist.barrier()
+            dist.destroy_process_group()
+            return
         got = _run_variants(lasp, qi, ki, vi, doi, s.to(dev))
         if mode == "golden":
             g = load_golden(p["name"])
@@ -167,3 +197,14 @@ def test_reference_test_shape_on_the_whole_box():
         p = dict(seed=90 + dp, dp=dp, sp=sp, b=2 * world, h=12, n=2048, d=128, e=64, slopes="alibi",
                  dtype="bfloat16", check_heads=[0, 5, 11], scale_qk=False)
         _launch(dp * sp, "oracle", p)
+
+
+def test_folded_preprocessing_across_ranks():
+    """lasp_fuse_parallel_fused on the whole box as one sequence-parallel group: elu(x)+1 and a scale folded into
+    the kernels that also hand the rank state over (bf16, config-1 shape per rank, raw N(0,1) q and k)."""
+    if _ngpu() < 2:
+        pytest.skip("needs >= 2 GPUs")
+    sp = _ngpu()
+    p = dict(seed=60, dp=1, sp=sp, b=2, h=12, n=2048 * sp, d=128, e=128, slopes="baseline", dtype="bfloat16",
+             check_heads=[0, 6, 11], scale_qk=False, fold=(128 ** -0.5, "elu1"))
+    _launch(sp, "fold", p)
