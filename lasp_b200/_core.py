@@ -35,14 +35,16 @@ def sliced_apply(fn, q, k, v, state_bufs=()):
     same way in the other direction (outputs of v slices are concatenated).
     ``state_bufs`` are (b,h,d,e) buffers sliced alongside.
 
-    When both widths are multiples of 128 the (q/k slice, v slice) pairs are stacked
-    along the batch dimension and go through ONE call - for a sequence-parallel
-    operator one state hand-over per direction instead of one per slice (the
-    reference runs a separate chain per slice, lasp/lasp_fuse.py:546-559).
+    For the sequence-parallel operators (those with state buffers), when both
+    widths are multiples of 128, the (q/k slice, v slice) pairs are stacked along
+    the batch dimension and go through ONE call: one state hand-over per direction
+    instead of one per slice (the reference runs a separate chain per slice,
+    lasp/lasp_fuse.py:546-559).  On a single device there is nothing to hand over
+    and the slices go one after the other, each with its spans spread over all SMs.
     """
     d, e = q.shape[-1], v.shape[-1]
     nd, ne = d // MAX_HEAD_SLICE, e // MAX_HEAD_SLICE
-    if d % MAX_HEAD_SLICE == 0 and e % MAX_HEAD_SLICE == 0 and nd * ne > 1:
+    if state_bufs and d % MAX_HEAD_SLICE == 0 and e % MAX_HEAD_SLICE == 0 and nd * ne > 1:
         b, h, n = q.shape[:3]
         w = MAX_HEAD_SLICE
 
