@@ -543,17 +543,20 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
     if (lane == 0) {
       int x_issued = 0;
       if (sums) {
-        // X of the first two tiles of the walk can come in during the sums
-        for (bool ok = w.start(blockIdx.x, gridDim.x); ok && x_issued < 2; ok = w.next(), ++x_issued) {
-          mbar_expect_tx(&x_full[x_issued], C * WX * 2);
-          tma_load_4d(sx[x_issued], &map_x, &x_full[x_issued], 0, w.t * C, 0, w.bh);
-        }
         for (int t = sum_t0, g = 0; t < sum_t1; ++t, ++g) {
           const int j = g & 1;
           if (g >= 2) wait_or_fault(&ring_empty[j], ((g >> 1) - 1) & 1, &dead, fault, kFaultMmaWait);
           mbar_expect_tx(&ring_full[j], C * (WX + WZ) * 2);
           tma_load_4d(sy[j], &map_y, &ring_full[j], 0, t * C, 0, my_bh);
           tma_load_4d(sz[j], &map_z, &ring_full[j], 0, t * C, 0, my_bh);
+          if (g == 1 || t == sum_t1 - 1) {
+            // X of the first two tiles of the walk can come in during the sums - behind the first ring
+            // stages, which every CTA of the launch asks for at the same moment and the sums wait for
+            for (bool ok = x_issued == 0 && w.start(blockIdx.x, gridDim.x); ok && x_issued < 2; ok = w.next(), ++x_issued) {
+              mbar_expect_tx(&x_full[x_issued], C * WX * 2);
+              tma_load_4d(sx[x_issued], &map_x, &x_full[x_issued], 0, w.t * C, 0, w.bh);
+            }
+          }
         }
         wait_or_fault(&sum_done, 0, &dead, fault, kFaultMmaWait);   // the MMAs have read every ring stage
       }
@@ -1069,19 +1072,19 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
     if (lane == 0) {
       bool first_qdo_issued = false;
       if (sums) {
-        // Q, dO of the first tile of the walk can come in during the sums
-        if (w.start(blockIdx.x, gridDim.x)) {
-          mbar_expect_tx(&qdo_full, C * (D + E) * 2);
-          tma_load_4d(sq, &map_q, &qdo_full, 0, w.t * C, 0, w.bh);
-          tma_load_4d(sdo, &map_do, &qdo_full, 0, w.t * C, 0, w.bh);
-          first_qdo_issued = true;
-        }
         for (int t = sum_t0, g = 0; t < sum_t1; ++t, ++g) {
           const int j = g & 1;
           if (g >= 2) wait_or_fault(&ring_empty[j], ((g >> 1) - 1) & 1, &dead, fault, kFaultMmaWait);
           mbar_expect_tx(&ring_full[j], C * (D + E) * 2);
           tma_load_4d(sk[j], &map_q, &ring_full[j], 0, t * C, 0, my_bh);
           tma_load_4d(sv[j], &map_do, &ring_full[j], 0, t * C, 0, my_bh);
+          // Q, dO of the first tile of the walk can come in during the sums, behind the first ring stages
+          if ((g == 1 || t == sum_t1 - 1) && !first_qdo_issued && w.start(blockIdx.x, gridDim.x)) {
+            mbar_expect_tx(&qdo_full, C * (D + E) * 2);
+            tma_load_4d(sq, &map_q, &qdo_full, 0, w.t * C, 0, w.bh);
+            tma_load_4d(sdo, &map_do, &qdo_full, 0, w.t * C, 0, w.bh);
+            first_qdo_issued = true;
+          }
         }
         wait_or_fault(&sum_done, 0, &dead, fault, kFaultMmaWait);   // the MMAs have read every ring stage
       }
