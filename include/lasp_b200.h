@@ -83,6 +83,11 @@ typedef struct {
   int32_t path;    /* lasp_path */
   int32_t qk_map;  /* lasp_qk_map */
   float qk_scale;  /* 0 is read as 1 */
+  /* Elements from one token's row to the next in q,k,dq,dk (pitch_d) and in v,o,do,dv (pitch_e); 0 = d / e, i.e.
+   * tensors of their own.  Larger values let a call work in place on a 128-wide slice of the head dimension of
+   * wider tensors (the slicing of lasp/lightning_attention.py:510-531 without a copy per slice): pass the address
+   * of the slice's first column.  Multiples of 8; tensor-core path only (LASP_ERR_PATH otherwise). */
+  int32_t pitch_d, pitch_e;
 } lasp_problem;
 
 /* Forward arguments.  ws = workspace of lasp_b200_fwd_workspace_bytes(); after

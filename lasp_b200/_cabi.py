@@ -32,7 +32,8 @@ class LaspStatusError(RuntimeError):
 
 
 class Problem(C.Structure):   # lasp_problem
-    _fields_ = [(n, C.c_int32) for n in ("b", "h", "n", "d", "e", "dtype", "path", "qk_map")] + [("qk_scale", C.c_float)]
+    _fields_ = ([(n, C.c_int32) for n in ("b", "h", "n", "d", "e", "dtype", "path", "qk_map")] + [("qk_scale", C.c_float)]
+                + [(n, C.c_int32) for n in ("pitch_d", "pitch_e")])
 
 
 QK_MAPS = {None: 0, "identity": 0, "elu1": 1}   # lasp_qk_map

@@ -122,26 +122,107 @@ def _check_shapes(q, k, v, s):
 
 class LightningAttention(torch.autograd.Function):
     """Single-device op: O = ((Q K^T) * M) V.  Interface of LightningAttention,
-    lasp/lightning_attention.py:396-504; gradients for q, k, v only."""
+    lasp/lightning_attention.py:396-504; gradients for q, k, v only.
+
+    Head dimensions wider than 128 are cut here, inside the function, the way the reference's wrapper cuts
+    them (lasp/lightning_attention.py:510-531: a sum over 128-wide q,k slices; v slices side by side) - but
+    the slices' results go straight into their place in o, dq, dk, dv.  Slicing outside, through autograd,
+    builds a full-size zero tensor per slice and adds them up: at d = e = 256 that costs more memory traffic
+    than the operator itself.
+    """
 
     @staticmethod
     def forward(ctx, q, k, v, s, qk_scale=1.0, feature_map=None):
         _check_shapes(q, k, v, s)
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        plan = _plan_for(q, v, qk_scale=qk_scale, feature_map=feature_map)
-        fw = ENGINE.Forward(plan, q, k, v, s)
-        o = fw.run()
-        ctx.plan = plan
-        ctx.fwd_ws = fw.ws
+        d, e = q.shape[-1], v.shape[-1]
+        ctx.pre = (qk_scale, feature_map)
         ctx.save_for_backward(q, k, v, s)
+        if d <= MAX_HEAD_SLICE and e <= MAX_HEAD_SLICE:
+            plan = _plan_for(q, v, qk_scale=qk_scale, feature_map=feature_map)
+            fw = ENGINE.Forward(plan, q, k, v, s)
+            ctx.pairs = None
+            ctx.plan, ctx.fwd_ws = plan, fw.ws
+            return fw.run()
+        o = torch.empty(*q.shape[:3], e, dtype=q.dtype, device=q.device)
+        # Where the kernels take a row pitch (tensor-core path), a slice is read and written where it lies in the
+        # wide tensors; otherwise it is copied out and back.
+        in_place = _slices_in_place(q, v, qk_scale, feature_map)
+        ctx.in_place = in_place
+        ctx.pairs = []                                   # (q/k slice, v slice, plan, forward workspace)
+        # in place, every tensor of a call has the wide tensors' row pitch: later contributions to a slice of o land
+        # in a slice of a second wide tensor and are added from there
+        more = torch.empty_like(o) if (in_place and len(_cuts(d)) > 1) else None
+        for e0, e1 in _cuts(e):
+            vs = v[..., e0:e1] if in_place else v[..., e0:e1].contiguous()
+            for i, (d0, d1) in enumerate(_cuts(d)):
+                qs, ks = (q[..., d0:d1], k[..., d0:d1]) if in_place else (q[..., d0:d1].contiguous(), k[..., d0:d1].contiguous())
+                plan = _slice_plan(q, v, d1 - d0, e1 - e0, qk_scale, feature_map, in_place)
+                first = i == 0
+                fw = ENGINE.Forward(plan, qs, ks, vs, s,
+                                    o=None if not in_place else (o if first else more)[..., e0:e1])
+                part = fw.run()
+                if not first:
+                    o[..., e0:e1] += part
+                elif not in_place:
+                    o[..., e0:e1] = part
+                ctx.pairs.append(((d0, d1), (e0, e1), plan, fw.ws))
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, s = ctx.saved_tensors
-        bw = ENGINE.Backward(ctx.plan, q, k, v, do.contiguous(), s, ctx.fwd_ws)
-        dq, dk, dv = bw.run()
+        do = do.contiguous()
+        if ctx.pairs is None:
+            bw = ENGINE.Backward(ctx.plan, q, k, v, do, s, ctx.fwd_ws)
+            dq, dk, dv = bw.run()
+            return dq, dk, dv, None, None, None
+        in_place = ctx.in_place
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        # (as in forward: later contributions go through second wide tensors with the same row pitch)
+        mq, mk, mv = (torch.empty_like(t) for t in (q, k, v)) if in_place else (None, None, None)
+        seen_d, seen_e = set(), set()
+        cut = (lambda t, lo, hi: t[..., lo:hi]) if in_place else (lambda t, lo, hi: t[..., lo:hi].contiguous())
+        for (d0, d1), (e0, e1), plan, fwd_ws in ctx.pairs:
+            new_d, new_e = d0 not in seen_d, e0 not in seen_e
+            # a q/k slice collects from every v slice, a v slice from every q/k slice: the first contribution is
+            # written in place (where the kernels can), the later ones are added
+            bw = ENGINE.Backward(plan, cut(q, d0, d1), cut(k, d0, d1), cut(v, e0, e1), cut(do, e0, e1), s, fwd_ws,
+                                 dq=None if not in_place else (dq if new_d else mq)[..., d0:d1],
+                                 dk=None if not in_place else (dk if new_d else mk)[..., d0:d1],
+                                 dv=None if not in_place else (dv if new_e else mv)[..., e0:e1])
+            gq, gk, gv = bw.run()
+            if not new_d:
+                dq[..., d0:d1] += gq
+                dk[..., d0:d1] += gk
+            elif not in_place:
+                dq[..., d0:d1] = gq
+                dk[..., d0:d1] = gk
+            if not new_e:
+                dv[..., e0:e1] += gv
+            elif not in_place:
+                dv[..., e0:e1] = gv
+            seen_d.add(d0), seen_e.add(e0)
         return dq, dk, dv, None, None, None
+
+
+def _slice_plan(q, v, wd, we, qk_scale, feature_map, in_place):
+    b, h, n = q.shape[:3]
+    pitches = dict(pitch_d=q.shape[-1], pitch_e=v.shape[-1]) if in_place else {}
+    if qk_scale == 1.0 and feature_map is None and not in_place:
+        return ENGINE.make_plan(b, h, n, wd, we, q.dtype)
+    return ENGINE.make_plan(b, h, n, wd, we, q.dtype, qk_scale=qk_scale, feature_map=feature_map, **pitches)
+
+
+def _slices_in_place(q, v, qk_scale, feature_map) -> bool:
+    """True when every (q/k slice, v slice) pair of these head dimensions can run on the wide tensors in place."""
+    try:
+        for d0, d1 in _cuts(q.shape[-1]):
+            for e0, e1 in _cuts(v.shape[-1]):
+                _slice_plan(q, v, d1 - d0, e1 - e0, qk_scale, feature_map, True)
+    except (ENGINE.LaspStatusError, TypeError):
+        return False
+    return True
 
 
 class SequenceParallelAttention(torch.autograd.Function):
@@ -278,9 +359,8 @@ def lightning_attn_fused(q, k, v, s, qk_scale: float = 1.0, feature_map=None):
     do this (fp32 path, head dims other than 64 / 128 per slice, more spans than SMs) get the same result from
     torch operations in front of the operator."""
     if (qk_scale == 1.0 and feature_map is None) or not kernels_preprocess(*_slice_like(q, v), qk_scale, feature_map):
-        return sliced_apply(lambda qs, ks, vs: LightningAttention.apply(qs, ks, vs, s),
-                            preprocess_qk(q, qk_scale, feature_map), preprocess_qk(k, qk_scale, feature_map), v)
-    return sliced_apply(lambda qs, ks, vs: LightningAttention.apply(qs, ks, vs, s, qk_scale, feature_map), q, k, v)
+        return LightningAttention.apply(preprocess_qk(q, qk_scale, feature_map), preprocess_qk(k, qk_scale, feature_map), v, s)
+    return LightningAttention.apply(q, k, v, s, qk_scale, feature_map)
 
 
 def sequence_parallel_fused(q, k, v, s, KV, DKV, qk_scale: float = 1.0, feature_map=None):

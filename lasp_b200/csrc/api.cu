@@ -83,6 +83,11 @@ int make_dims(const lasp_problem* p, lasp::Dims* m) {
   m->b = p->b; m->h = p->h; m->n = p->n; m->d = p->d; m->e = p->e;
   m->dtype = p->dtype;
   if (p->qk_map != LASP_QK_IDENTITY && p->qk_map != LASP_QK_ELU1) return LASP_ERR_SHAPE;
+  if (p->pitch_d < 0 || p->pitch_e < 0 || (p->pitch_d && p->pitch_d < p->d) || (p->pitch_e && p->pitch_e < p->e) ||
+      p->pitch_d % 8 || p->pitch_e % 8)
+    return LASP_ERR_SHAPE;
+  m->pitch_d = p->pitch_d ? p->pitch_d : p->d;
+  m->pitch_e = p->pitch_e ? p->pitch_e : p->e;
   m->qk_map = p->qk_map;
   m->qk_scale = p->qk_scale == 0.f ? 1.f : p->qk_scale;
   m->walk = 0;
@@ -96,6 +101,7 @@ int make_dims(const lasp_problem* p, lasp::Dims* m) {
   m->path = path;
   if (path == LASP_PATH_SIMT) {
     if (lasp::has_qk_preprocessing(*m)) return LASP_ERR_PATH;   // folded into the tensor-core kernels only
+    if (m->pitch_d != m->d || m->pitch_e != m->e) return LASP_ERR_PATH;   // slices in place: TMA tensor maps only
     m->chunk = lasp::kSimtChunk;
     m->nc = (p->n + m->chunk - 1) / m->chunk;
     return LASP_OK;

@@ -35,6 +35,7 @@ struct Dims {
   int walk;   // 1 on the tensor path: the state is carried on chip along a span of tiles
   int tiles;  // tensor path: 128-token tiles per sequence
   int span;   // tensor path: tiles per span (chunk = span * 128)
+  int pitch_d, pitch_e;  // elements between the rows of consecutive tokens in q,k,dq,dk and in v,o,do,dv
   int qk_map;      // q and k enter as qk_scale * map(x): 0 identity, 1 elu(x) + 1
   float qk_scale;  // (1 when the caller left it 0)
 };

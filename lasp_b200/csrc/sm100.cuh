@@ -307,13 +307,15 @@ inline cudaError_t make_tile_map(CUtensorMap* map, const void* base, uint64_t ro
 
 // tensor map of `seqs` row-major bf16 matrices [n x width] lying one after the other,
 // box = {64, box_rows, width/64, 1}: a tile never crosses from one sequence into the next
+// `pitch`: elements from one token's row to the next (= width for a tensor of its own; larger for a slice of the
+// head dimension of a wider tensor, which is then read and written in place)
 inline cudaError_t make_seq_tile_map(CUtensorMap* map, const void* base, uint64_t seqs, uint64_t n, uint32_t width,
-                                     uint32_t box_rows) {
+                                     uint32_t box_rows, uint32_t pitch) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return cudaErrorNotSupported;
-  if (width % 64 || box_rows > 256 || n == 0 || seqs == 0) return cudaErrorInvalidValue;
+  if (width % 64 || box_rows > 256 || n == 0 || seqs == 0 || pitch < width || pitch % 8) return cudaErrorInvalidValue;
   const cuuint64_t dims[4] = {64, n, width / 64, seqs};
-  const cuuint64_t strides[3] = {(cuuint64_t)width * 2, 128, (cuuint64_t)n * width * 2};  // bytes, dims 1..3
+  const cuuint64_t strides[3] = {(cuuint64_t)pitch * 2, 128, (cuuint64_t)n * pitch * 2};  // bytes, dims 1..3
   const cuuint32_t box[4] = {64, box_rows, width / 64, 1};
   const cuuint32_t elem[4] = {1, 1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,

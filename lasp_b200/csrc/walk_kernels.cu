@@ -407,6 +407,7 @@ struct WalkArgs {
   float qk_scale;      // q and k enter as qk_scale * map(q), qk_scale * map(k)
   int elu;             // map = elu(x) + 1 (otherwise the identity)
   const void* raw;     // backward with a map or a scale: the raw q (dQ walk) or k (dK/dV walk) for the chain rule
+  int raw_pitch;       // ... and its row pitch in elements
   int even;            // the tiles of a sequence are shared out evenly among its spans (see TileWalk); a fused
                        // forward records it in sync[kSyncEven], the dQ walk reads it from the forward's workspace
   const uint32_t* even_word;   // dQ: where the forward pass recorded how it cut the sequences (NULL: a.even)
@@ -923,7 +924,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
         // dq = dq' * c * map'(q), q read from the raw tensor (rows past the end of the sequence are not stored)
         const bool live = row < len;
         const __nv_bfloat16* raw =
-            static_cast<const __nv_bfloat16*>(a.raw) + ((size_t)w.bh * a.n + (size_t)w.t * C + (live ? row : 0)) * WZ;
+            static_cast<const __nv_bfloat16*>(a.raw) + ((size_t)w.bh * a.n + (size_t)w.t * C + (live ? row : 0)) * a.raw_pitch;
 #pragma unroll 1
         for (int cc = 0; cc < WZ / 64; ++cc) {
           const int col0 = half * (WZ / 2) + cc * 32;
@@ -1411,7 +1412,7 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
         // dk = dk' * c * map'(k), k read from the raw tensor (rows past the end of the sequence are not stored)
         const bool live = row < len;
         const __nv_bfloat16* raw =
-            static_cast<const __nv_bfloat16*>(a.raw) + ((size_t)w.bh * a.n + (size_t)w.t * C + (live ? row : 0)) * D;
+            static_cast<const __nv_bfloat16*>(a.raw) + ((size_t)w.bh * a.n + (size_t)w.t * C + (live ? row : 0)) * a.raw_pitch;
 #pragma unroll 1
         for (int cc = 0; cc < D / 64; ++cc) {
           const int col0 = half * (D / 2) + cc * 32;
@@ -1465,8 +1466,8 @@ cudaError_t opt_in_smem(F* fn, size_t bytes) {
   return err;
 }
 
-cudaError_t seq_map(CUtensorMap* map, const void* base, const Dims& m, int width, const char* what) {
-  cudaError_t err = make_seq_tile_map(map, base, (uint64_t)m.b * m.h, (uint64_t)m.n, (uint32_t)width, C);
+cudaError_t seq_map(CUtensorMap* map, const void* base, const Dims& m, int width, int pitch, const char* what) {
+  cudaError_t err = make_seq_tile_map(map, base, (uint64_t)m.b * m.h, (uint64_t)m.n, (uint32_t)width, C, (uint32_t)pitch);
   if (err != cudaSuccess) {
     static thread_local char text[160];
     snprintf(text, sizeof(text), "tensor map (%s): CUresult %d, base %p, b*h %d, n %d, width %d", what,
@@ -1492,8 +1493,8 @@ cudaError_t launch_span_totals(const Dims& m, const void* a, const void* bten, c
                                bool reverse, cudaStream_t st) {
   CUtensorMap ma, mb;
   cudaError_t err;
-  if ((err = seq_map(&ma, a, m, D, "span totals, first operand")) != cudaSuccess) return err;
-  if ((err = seq_map(&mb, bten, m, E, "span totals, second operand")) != cudaSuccess) return err;
+  if ((err = seq_map(&ma, a, m, D, m.pitch_d, "span totals, first operand")) != cudaSuccess) return err;
+  if ((err = seq_map(&mb, bten, m, E, m.pitch_e, "span totals, second operand")) != cudaSuccess) return err;
   int32_t* fault = nullptr;
   if ((err = fault_word_address(&fault)) != cudaSuccess) return err;
   const size_t smem = (size_t)3 * C * (D + E) * 2 + 1024;
@@ -1525,16 +1526,16 @@ cudaError_t launch_walk_out_pre(const Dims& m, const void* x, const void* y, con
   constexpr int WX = DQ ? E : D, WZ = DQ ? D : E;
   CUtensorMap mx, my, mz, mo;
   cudaError_t err;
-  if ((err = seq_map(&mx, x, m, WX, DQ ? "do" : "q")) != cudaSuccess) return err;
-  if ((err = seq_map(&my, y, m, WX, DQ ? "v" : "k")) != cudaSuccess) return err;
-  if ((err = seq_map(&mz, z, m, WZ, DQ ? "k" : "v")) != cudaSuccess) return err;
-  if ((err = seq_map(&mo, out, m, WZ, DQ ? "dq" : "o")) != cudaSuccess) return err;
+  if ((err = seq_map(&mx, x, m, WX, DQ ? m.pitch_e : m.pitch_d, DQ ? "do" : "q")) != cudaSuccess) return err;
+  if ((err = seq_map(&my, y, m, WX, DQ ? m.pitch_e : m.pitch_d, DQ ? "v" : "k")) != cudaSuccess) return err;
+  if ((err = seq_map(&mz, z, m, WZ, DQ ? m.pitch_d : m.pitch_e, DQ ? "k" : "v")) != cudaSuccess) return err;
+  if ((err = seq_map(&mo, out, m, WZ, DQ ? m.pitch_d : m.pitch_e, DQ ? "dq" : "o")) != cudaSuccess) return err;
   if ((err = fault_word_address(&a.fault)) != cudaSuccess) return err;
   const size_t smem = (size_t)7 * kBuf + 1024;
   if ((err = opt_in_smem(k_walk_out<D, E, DQ, FUSED, PRE, LINK>, smem)) != cudaSuccess) return err;
   a.h = m.h, a.n = m.n, a.tiles = m.tiles, a.span = m.span, a.nspans = m.nc, a.items = m.b * m.h * m.nc;
   a.wait_clocks = kFlagWaitClocks;
-  a.qk_scale = m.qk_scale, a.elu = m.qk_map;
+  a.qk_scale = m.qk_scale, a.elu = m.qk_map, a.raw_pitch = m.pitch_d;
   const bool waits = FUSED && (m.nc > 1 || a.link.ranks > 0);   // CTAs wait for one another: one span each, all resident
   a.coop = waits ? 1 : 0;
   if (waits) a.even = 1;
@@ -1556,19 +1557,19 @@ cudaError_t launch_walk_dkv_pre(const Dims& m, const void* q, const void* k, con
                             void* dv, WalkArgs a, cudaStream_t st) {
   CUtensorMap mq, mk, mv, mdo, mdk, mdv;
   cudaError_t err;
-  if ((err = seq_map(&mq, q, m, D, "q")) != cudaSuccess) return err;
-  if ((err = seq_map(&mk, k, m, D, "k")) != cudaSuccess) return err;
-  if ((err = seq_map(&mv, v, m, E, "v")) != cudaSuccess) return err;
-  if ((err = seq_map(&mdo, d_o, m, E, "do")) != cudaSuccess) return err;
-  if ((err = seq_map(&mdk, dk, m, D, "dk")) != cudaSuccess) return err;
-  if ((err = seq_map(&mdv, dv, m, E, "dv")) != cudaSuccess) return err;
+  if ((err = seq_map(&mq, q, m, D, m.pitch_d, "q")) != cudaSuccess) return err;
+  if ((err = seq_map(&mk, k, m, D, m.pitch_d, "k")) != cudaSuccess) return err;
+  if ((err = seq_map(&mv, v, m, E, m.pitch_e, "v")) != cudaSuccess) return err;
+  if ((err = seq_map(&mdo, d_o, m, E, m.pitch_e, "do")) != cudaSuccess) return err;
+  if ((err = seq_map(&mdk, dk, m, D, m.pitch_d, "dk")) != cudaSuccess) return err;
+  if ((err = seq_map(&mdv, dv, m, E, m.pitch_e, "dv")) != cudaSuccess) return err;
   if ((err = fault_word_address(&a.fault)) != cudaSuccess) return err;
   a.raw = k;   // for the chain rule of a folded k preprocessing
   const size_t smem = (size_t)7 * kBuf + 1024;
   if ((err = opt_in_smem(k_walk_dkv<D, E, FUSED, PRE, LINK>, smem)) != cudaSuccess) return err;
   a.h = m.h, a.n = m.n, a.tiles = m.tiles, a.span = m.span, a.nspans = m.nc, a.items = m.b * m.h * m.nc;
   a.wait_clocks = kFlagWaitClocks;
-  a.qk_scale = m.qk_scale, a.elu = m.qk_map;
+  a.qk_scale = m.qk_scale, a.elu = m.qk_map, a.raw_pitch = m.pitch_d;
   const bool waits = FUSED && (m.nc > 1 || a.link.ranks > 0);
   a.coop = waits ? 1 : 0;
   if (waits) a.even = 1;

@@ -50,6 +50,21 @@ def _ptr(t):
     return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
 
 
+def _check_layout(plan, **tensors):
+    """Every (b,h,n,width) tensor of a call must have the row pitch the plan was made for (the kernels address it
+    by that pitch alone): raises instead of letting a kernel write past a buffer."""
+    for name, t in tensors.items():
+        if t is None:
+            continue
+        wide = name in ("v", "o", "do", "dv")
+        width = plan.e if wide else plan.d
+        pitch = (plan.problem.pitch_e if wide else plan.problem.pitch_d) or width
+        want = (plan.h * plan.n * pitch, plan.n * pitch, pitch, 1)
+        if tuple(t.shape) != (plan.b, plan.h, plan.n, width) or tuple(t.stride()) != want:
+            raise ValueError(f"{name}: shape {tuple(t.shape)} strides {tuple(t.stride())}; this plan needs shape "
+                             f"{(plan.b, plan.h, plan.n, width)} with strides {want}")
+
+
 def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
@@ -98,10 +113,11 @@ def _require_cuda(*ts):
 
 
 def make_plan(b: int, h: int, n: int, d: int, e: int, dtype: torch.dtype, path: str | None = None,
-              qk_scale: float = 1.0, feature_map: str | None = None) -> Plan:
+              qk_scale: float = 1.0, feature_map: str | None = None, pitch_d: int = 0, pitch_e: int = 0) -> Plan:
     """``qk_scale`` / ``feature_map`` ("elu1"): the operator is evaluated on qk_scale * map(q), qk_scale * map(k)
     inside the kernels (lasp_problem.qk_map, .qk_scale); raises LaspStatusError when the problem's kernels
-    cannot do that."""
+    cannot do that.  ``pitch_d`` / ``pitch_e``: row pitch in elements of q,k,dq,dk / v,o,do,dv when they are slices
+    of the head dimension of wider tensors (0: tensors of their own); tensor-core path only."""
     if dtype not in _DTYPES:
         raise TypeError(f"unsupported dtype {dtype}; use float32, bfloat16 or float16")
     name = path or default_path()
@@ -109,7 +125,8 @@ def make_plan(b: int, h: int, n: int, d: int, e: int, dtype: torch.dtype, path: 
         raise ValueError(f"unknown kernel path {name!r}; use auto, simt or tensor")
     if feature_map not in _cabi.QK_MAPS:
         raise ValueError(f"unknown feature map {feature_map!r}; use None or 'elu1'")
-    prob = _cabi.Problem(b, h, n, d, e, _DTYPES[dtype], _PATHS[name], _cabi.QK_MAPS[feature_map], float(qk_scale))
+    prob = _cabi.Problem(b, h, n, d, e, _DTYPES[dtype], _PATHS[name], _cabi.QK_MAPS[feature_map], float(qk_scale),
+                         int(pitch_d), int(pitch_e))
     resolved = _cabi.call("lasp_b200_resolve_path", C.byref(prob))
     prob.path = resolved
     chunk = _cabi.call("lasp_b200_chunk_tokens", C.byref(prob))
@@ -146,6 +163,7 @@ class Forward:
         self.s = _slopes(s, plan.h, q.device)
         self.kv_in, self.kv_out = kv_in, kv_out
         self.o = o if o is not None else torch.empty(plan.b, plan.h, plan.n, plan.e, dtype=q.dtype, device=q.device)
+        _check_layout(plan, q=q, k=k, v=v, o=self.o)
         self.ws = ws if ws is not None else new_workspace(plan, q.device)
         self._args = _cabi.FwdArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(self.s), _ptr(kv_in), _ptr(kv_out),
                                    _ptr(self.o), _ptr(self.ws), self.ws.numel())
@@ -178,12 +196,16 @@ class Forward:
 class Backward:
     """One backward call split in its three phases."""
 
-    def __init__(self, plan: Plan, q, k, v, do, s, fwd_ws, dkv_in=None, dkv_out=None, ws=None):
+    def __init__(self, plan: Plan, q, k, v, do, s, fwd_ws, dkv_in=None, dkv_out=None, ws=None, dq=None, dk=None,
+                 dv=None):
         _require_cuda(q, k, v, do, fwd_ws, dkv_in, dkv_out)
         self.plan = plan
         self.s = _slopes(s, plan.h, q.device)
         self.keep = (q, k, v, do, fwd_ws, dkv_in, dkv_out)
-        self.dq, self.dk, self.dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        self.dq = dq if dq is not None else torch.empty_like(q)
+        self.dk = dk if dk is not None else torch.empty_like(k)
+        self.dv = dv if dv is not None else torch.empty_like(v)
+        _check_layout(plan, q=q, k=k, v=v, do=do, dq=self.dq, dk=self.dk, dv=self.dv)
         self.ws = ws if ws is not None else new_workspace(plan, q.device)
         self._args = _cabi.BwdArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(do), _ptr(self.s), _ptr(dkv_in), _ptr(dkv_out),
                                    _ptr(self.dq), _ptr(self.dk), _ptr(self.dv), _ptr(fwd_ws), fwd_ws.numel(),

@@ -3,7 +3,7 @@
 Drop-in for ``lasp/lightning_attention.py`` of the reference: ``lightning_attn``
 (:510-531) and ``lightning_attn_`` (= the autograd function's ``apply``, :507).
 """
-from ._core import LightningAttention, sliced_apply
+from ._core import LightningAttention
 
 lightning_attn_ = LightningAttention.apply
 
@@ -15,4 +15,4 @@ def lightning_attn(q, k, v, ed):
     (b, h, n, e) in q's dtype.  Any n; d and e multiples of 16 (wider than 128
     is sliced).  No scaling, no normaliser: exactly the reference's op.
     """
-    return sliced_apply(lambda qs, ks, vs: lightning_attn_(qs, ks, vs, ed), q, k, v)
+    return lightning_attn_(q, k, v, ed)

@@ -489,6 +489,29 @@ def test_folded_preprocessing_falls_back_to_torch_where_the_kernels_cannot():
         assert O.max_rel_err(t, w) < TOL_FP32, key
 
 
+def test_wide_heads_run_in_place_and_a_wrong_pitch_is_refused():
+    """d = e = 256 in bf16: the 128-wide slice pairs run on the wide tensors in place (row pitch 256), and a tensor
+    whose pitch is not the plan's is refused before anything is launched."""
+    from lasp_b200 import _core, engine
+    b, h, n = 1, 2, 256
+    q, k, v, do = (t.to(DEV, torch.bfloat16) for t in O.make_inputs(5, b, h, n, 256, 256))
+    assert _core._slices_in_place(q, v, 1.0, None)
+    plan = engine.make_plan(b, h, n, 128, 128, torch.bfloat16, pitch_d=256, pitch_e=256)
+    s = O.baseline_slopes(h)
+    with pytest.raises(ValueError):
+        engine.Forward(plan, q[..., :128], k[..., :128], v[..., :128], s)          # o would be a tensor of its own
+    with pytest.raises(ValueError):
+        engine.Forward(plan, q[..., :128].contiguous(), k[..., :128], v[..., :128], s, o=torch.empty_like(v)[..., :128])
+    canary = torch.full_like(v, 7.0)
+    fw = engine.Forward(plan, q[..., 128:], k[..., 128:], v[..., :128], s, o=canary[..., 128:])
+    fw.run()
+    torch.cuda.synchronize()
+    assert bool((canary[..., :128] == 7.0).all())                                   # the other half is untouched
+    ref = O.blocked_forward(q[..., 128:].float().cpu(), k[..., 128:].float().cpu(), v[..., :128].float().cpu(), s)[0]
+    assert O.max_rel_err(canary[..., 128:].float().cpu(), ref) < TOL_BF16
+    assert engine.read_status() == 0
+
+
 def test_exchange_wait_runs_out_and_is_reported():
     """Failure detection without a GPU fault: the last rank of a group of two whose sender never writes.  The
     hand-over kernel's waits are bounded, so it must come back on its own, set the relay bit (4) of the fault
