@@ -483,9 +483,19 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
   __shared__ int dead;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int32_t* fault = a.fault;
+  // Thread 0 is also the producer: it asks for its first tiles before the CTA-wide barrier below, so that their
+  // flight overlaps the rest of the set-up (what it issued is remembered in early_*; only its copy matters).
+  bool early_ring = false;
+  int early_x = 0;
   if (tid == 0) {
     dead = 0;
-    even_s = a.even_word != nullptr ? ld_volatile_u32(a.even_word) : (uint32_t)a.even;
+    // the words this launch reads from global memory, all in flight while the barriers are set up
+    const uint32_t ev = a.even_word != nullptr ? ld_volatile_u32(a.even_word) : (uint32_t)a.even;
+    uint32_t ss = 0, sx_ = 0;
+    if constexpr (FUSED) {
+      if (a.coop) ss = ld_volatile_u32(a.sync);
+      if (LINK && a.link.ranks > 0) sx_ = ld_volatile_u32(a.link.counters);
+    }
     for (int p = 0; p < 2; ++p) {
       mbar_init(&x_full[p], 1);
       mbar_init(&y_full[p], 1);
@@ -512,9 +522,24 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
     prefetch_tensormap(&map_y);
     prefetch_tensormap(&map_z);
     prefetch_tensormap(&map_out);
+    even_s = ev;
     if constexpr (FUSED) {
-      step_s = a.coop ? ld_volatile_u32(a.sync) + 1 : 0;                       // this launch among those on the workspace
-      step_x = LINK && a.link.ranks > 0 ? ld_volatile_u32(a.link.counters) + 1 : 0;    // this hand-over in the group
+      step_s = a.coop ? ss + 1 : 0;                              // this launch among those on the workspace
+      step_x = LINK && a.link.ranks > 0 ? sx_ + 1 : 0;           // this hand-over in the group
+    }
+    TileWalk w0{a.items, a.nspans, a.span, a.tiles, 0, false, ev != 0};
+    if (w0.start(blockIdx.x, gridDim.x)) {
+      const int sp0 = w0.it - w0.bh * a.nspans;
+      if (FUSED && a.coop && (sp0 < a.nspans - 1 || a.all_totals)) {   // first stage of the span-total ring
+        mbar_expect_tx(&ring_full[0], C * (WX + WZ) * 2);
+        tma_load_4d(smem + 2 * kBuf, &map_y, &ring_full[0], 0, w0.t0 * C, 0, w0.bh);
+        tma_load_4d(smem + 4 * kBuf, &map_z, &ring_full[0], 0, w0.t0 * C, 0, w0.bh);
+        early_ring = true;
+      } else {                                                          // X of the first tile of the walk
+        mbar_expect_tx(&x_full[0], C * WX * 2);
+        tma_load_4d(smem, &map_x, &x_full[0], 0, w0.t * C, 0, w0.bh);
+        early_x = 1;
+      }
     }
   }
   if (warp == 2) tmem_alloc(&tmem_slot, 512);
@@ -542,14 +567,16 @@ __global__ void __launch_bounds__(320, 1) k_walk_out(const __grid_constant__ CUt
 
   if (warp == 0) {
     if (lane == 0) {
-      int x_issued = 0;
+      int x_issued = early_x;
       if (sums) {
         for (int t = sum_t0, g = 0; t < sum_t1; ++t, ++g) {
           const int j = g & 1;
           if (g >= 2) wait_or_fault(&ring_empty[j], ((g >> 1) - 1) & 1, &dead, fault, kFaultMmaWait);
-          mbar_expect_tx(&ring_full[j], C * (WX + WZ) * 2);
-          tma_load_4d(sy[j], &map_y, &ring_full[j], 0, t * C, 0, my_bh);
-          tma_load_4d(sz[j], &map_z, &ring_full[j], 0, t * C, 0, my_bh);
+          if (!(g == 0 && early_ring)) {
+            mbar_expect_tx(&ring_full[j], C * (WX + WZ) * 2);
+            tma_load_4d(sy[j], &map_y, &ring_full[j], 0, t * C, 0, my_bh);
+            tma_load_4d(sz[j], &map_z, &ring_full[j], 0, t * C, 0, my_bh);
+          }
           if (g == 1 || t == sum_t1 - 1) {
             // X of the first two tiles of the walk can come in during the sums - behind the first ring
             // stages, which every CTA of the launch asks for at the same moment and the sums wait for
@@ -1016,8 +1043,15 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
   __shared__ int dead;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int32_t* fault = a.fault;
+  // thread 0 is also the producer: its first loads go out before the CTA-wide barrier (see k_walk_out)
+  bool early_ring = false, early_kv = false;
   if (tid == 0) {
     dead = 0;
+    uint32_t ss = 0, sx_ = 0;   // in flight while the barriers are set up
+    if constexpr (FUSED) {
+      if (a.coop) ss = ld_volatile_u32(a.sync);
+      if (LINK && a.link.ranks > 0) sx_ = ld_volatile_u32(a.link.counters);
+    }
     for (int p = 0; p < 2; ++p) {
       mbar_init(&kv_full[p], 1);
       mbar_init(&staged[p], kWorkers);
@@ -1044,8 +1078,23 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
     prefetch_tensormap(&map_dk);
     prefetch_tensormap(&map_dv);
     if constexpr (FUSED) {
-      step_s = a.coop ? ld_volatile_u32(a.sync) + 1 : 0;                       // this launch among those on the workspace
-      step_x = LINK && a.link.ranks > 0 ? ld_volatile_u32(a.link.counters) + 1 : 0;    // this hand-over in the group
+      step_s = a.coop ? ss + 1 : 0;                              // this launch among those on the workspace
+      step_x = LINK && a.link.ranks > 0 ? sx_ + 1 : 0;           // this hand-over in the group
+    }
+    TileWalk w0{a.items, a.nspans, a.span, a.tiles, 0, true, a.even != 0};
+    if (w0.start(blockIdx.x, gridDim.x)) {
+      const int sp0 = w0.it - w0.bh * a.nspans;
+      if (FUSED && a.coop && (sp0 > 0 || a.all_totals)) {   // first stage of the span-total ring: Q, dO
+        mbar_expect_tx(&ring_full[0], C * (D + E) * 2);
+        tma_load_4d(smem + 2 * kBuf, &map_q, &ring_full[0], 0, w0.t0 * C, 0, w0.bh);
+        tma_load_4d(smem + 4 * kBuf, &map_do, &ring_full[0], 0, w0.t0 * C, 0, w0.bh);
+        early_ring = true;
+      } else {                                               // K, V of the first tile of the walk
+        mbar_expect_tx(&kv_full[0], C * (D + E) * 2);
+        tma_load_4d(smem + 2 * kBuf, &map_k, &kv_full[0], 0, w0.t * C, 0, w0.bh);
+        tma_load_4d(smem + 4 * kBuf, &map_v, &kv_full[0], 0, w0.t * C, 0, w0.bh);
+        early_kv = true;
+      }
     }
   }
   if (warp == 2) tmem_alloc(&tmem_slot, 512);
@@ -1076,9 +1125,11 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
         for (int t = sum_t0, g = 0; t < sum_t1; ++t, ++g) {
           const int j = g & 1;
           if (g >= 2) wait_or_fault(&ring_empty[j], ((g >> 1) - 1) & 1, &dead, fault, kFaultMmaWait);
-          mbar_expect_tx(&ring_full[j], C * (D + E) * 2);
-          tma_load_4d(sk[j], &map_q, &ring_full[j], 0, t * C, 0, my_bh);
-          tma_load_4d(sv[j], &map_do, &ring_full[j], 0, t * C, 0, my_bh);
+          if (!(g == 0 && early_ring)) {
+            mbar_expect_tx(&ring_full[j], C * (D + E) * 2);
+            tma_load_4d(sk[j], &map_q, &ring_full[j], 0, t * C, 0, my_bh);
+            tma_load_4d(sv[j], &map_do, &ring_full[j], 0, t * C, 0, my_bh);
+          }
           // Q, dO of the first tile of the walk can come in during the sums, behind the first ring stages
           if ((g == 1 || t == sum_t1 - 1) && !first_qdo_issued && w.start(blockIdx.x, gridDim.x)) {
             mbar_expect_tx(&qdo_full, C * (D + E) * 2);
@@ -1101,9 +1152,11 @@ __global__ void __launch_bounds__(320, 1) k_walk_dkv(
           bulk_commit();
           bulk_wait_read<0>();
         }
-        mbar_expect_tx(&kv_full[p], C * (D + E) * 2);
-        tma_load_4d(sk[p], &map_k, &kv_full[p], 0, w.t * C, 0, w.bh);
-        tma_load_4d(sv[p], &map_v, &kv_full[p], 0, w.t * C, 0, w.bh);
+        if (!(i == 0 && early_kv)) {
+          mbar_expect_tx(&kv_full[p], C * (D + E) * 2);
+          tma_load_4d(sk[p], &map_k, &kv_full[p], 0, w.t * C, 0, w.bh);
+          tma_load_4d(sv[p], &map_v, &kv_full[p], 0, w.t * C, 0, w.bh);
+        }
         if (i >= 1) {   // Q, dO of tile i-1 are read: by phase B and by L
           wait_or_fault(&b_done, (i - 1) & 1, &dead, fault, kFaultMmaWait);
           wait_or_fault(&l_done, (i - 1) & 1, &dead, fault, kFaultMmaWait);
