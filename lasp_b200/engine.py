@@ -60,7 +60,9 @@ def _check_layout(plan, **tensors):
         width = plan.e if wide else plan.d
         pitch = (plan.problem.pitch_e if wide else plan.problem.pitch_d) or width
         want = (plan.h * plan.n * pitch, plan.n * pitch, pitch, 1)
-        if tuple(t.shape) != (plan.b, plan.h, plan.n, width) or tuple(t.stride()) != want:
+        # (the stride of a dimension of extent 1 is never used and may be anything)
+        strides_ok = all(st == w or ext == 1 for st, w, ext in zip(t.stride(), want, t.shape))
+        if tuple(t.shape) != (plan.b, plan.h, plan.n, width) or not strides_ok:
             raise ValueError(f"{name}: shape {tuple(t.shape)} strides {tuple(t.stride())}; this plan needs shape "
                              f"{(plan.b, plan.h, plan.n, width)} with strides {want}")
 
