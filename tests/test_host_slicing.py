@@ -75,3 +75,25 @@ def test_ragged_lengths_blocked_equals_dense(n, seed):
     o2, _ = O.blocked_forward(q2, k2, v2, s, kv, dtype=torch.float64)
     whole = O.dense_closed_form(torch.cat([q, q2], 2), torch.cat([k, k2], 2), torch.cat([v, v2], 2), s)
     assert O.max_rel_err(o2, whole[:, :, n:]) < 1e-10
+
+
+def test_layout_check_of_a_call():
+    """The guard in front of every launch: tensors must have the row pitch their plan was made for; strides of
+    unit dimensions do not count (a chunk cut out of a longer sequence keeps the long sequence's strides)."""
+    from types import SimpleNamespace
+    from lasp_b200 import engine
+    b, h, n = 1, 1, 128
+    plan = SimpleNamespace(b=b, h=h, n=n, d=64, e=64, problem=SimpleNamespace(pitch_d=0, pitch_e=0))
+    whole = torch.zeros(b, h, 2 * n, 64)
+    chunk = whole[:, :, n:]                                   # contiguous rows, batch/head strides of the long tensor
+    engine._check_layout(plan, q=chunk, k=chunk.contiguous(), v=chunk, o=None)
+    wide = torch.zeros(b, h, n, 256)
+    with pytest.raises(ValueError):
+        engine._check_layout(plan, q=wide[..., :64])          # row pitch 256, plan says 64
+    with pytest.raises(ValueError):
+        engine._check_layout(plan, q=torch.zeros(b, h, n, 32))
+    sliced = SimpleNamespace(b=2, h=3, n=n, d=128, e=128, problem=SimpleNamespace(pitch_d=256, pitch_e=256))
+    wide = torch.zeros(2, 3, n, 256)
+    engine._check_layout(sliced, q=wide[..., 128:], dv=wide[..., :128])
+    with pytest.raises(ValueError):
+        engine._check_layout(sliced, q=wide[..., 128:].contiguous())
